@@ -1,0 +1,279 @@
+// extern "C" boundary: argument validation, launch geometry, dispatch.  See
+// include/dcnv4_b200.h for the contract of every entry point and the reference interface
+// each one replaces.
+#include "../../include/dcnv4_b200.h"
+
+#include <mutex>
+
+#include "common.cuh"
+
+using namespace dcnb200;
+
+namespace {
+
+// One status word per device; kernels that give up on a bounded wait record it here.
+__device__ int g_status_word;
+
+constexpr int kMaxDevices = 64;
+std::mutex g_mu;
+int* g_status_ptr[kMaxDevices] = {nullptr};
+
+int status_ptr(int** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return DCNV4B200_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_status_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_status_word);
+    if (e != cudaSuccess) return (int)e;
+    g_status_ptr[dev] = static_cast<int*>(p);
+  }
+  *out = g_status_ptr[dev];
+  return 0;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int elem_size(int dtype) { return dtype == DCNV4B200_F32 ? 4 : 2; }
+inline int vec_len(int dtype) { return dtype == DCNV4B200_F32 ? 4 : 8; }
+inline bool dtype_ok(int dtype) { return dtype >= DCNV4B200_F32 && dtype <= DCNV4B200_BF16; }
+
+// D == vec * tpg * chunks with tpg the largest power of two (<= 32) dividing D/vec.
+int split_channels(int D, int dtype, int* tpg, int* chunks) {
+  const int v = vec_len(dtype);
+  if (D <= 0 || D % v != 0) return DCNV4B200_ERR_CHANNELS;
+  const int nvec = D / v;
+  int t = 1;
+  while (t < 32 && nvec % (t * 2) == 0) t *= 2;
+  *tpg = t;
+  *chunks = nvec / t;
+  return 0;
+}
+
+// Queries per CTA: as many as fit the staging budget, but never so many that the grid
+// drops below a few CTAs per SM; `unit` keeps every tile start 16-byte aligned.
+int pick_tile(long long nq, size_t bytes_per_query, int unit, int items_per_query) {
+  long long t = (long long)(kStageBytesMax / bytes_per_query);
+  const long long cap_items = (4LL * kThreads + items_per_query - 1) / items_per_query;  // ~4 items per thread
+  if (t > cap_items) t = cap_items;
+  const long long cap_grid = nq / (148LL * 4);
+  if (cap_grid >= 1 && t > cap_grid) t = cap_grid;
+  if (t > 64) t = 64;
+  t = (t / unit) * unit;
+  if (t < unit) t = unit;
+  return (int)t;
+}
+
+int fill_dcn(DcnParams& p, int dtype, int N, int H, int W, int G, int D, int kh, int kw, int sh, int sw,
+             int ph, int pw, int dh, int dw, float offset_scale, int remove_center, int Ppad, int softmax,
+             bool backward) {
+  if (!dtype_ok(dtype)) return DCNV4B200_ERR_DTYPE;
+  if (N <= 0 || H <= 0 || W <= 0 || G <= 0 || D <= 0 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 ||
+      ph < 0 || pw < 0 || dh <= 0 || dw <= 0)
+    return DCNV4B200_ERR_SHAPE;
+  const int Ho = dcnv4b200_out_size(H, ph, dh, kh, sh), Wo = dcnv4b200_out_size(W, pw, dw, kw, sw);
+  if (Ho <= 0 || Wo <= 0) return DCNV4B200_ERR_SHAPE;
+  const int K = kh * kw - (remove_center ? 1 : 0);
+  if (K <= 0) return DCNV4B200_ERR_SHAPE;
+  if (Ppad % 8 != 0 || (long long)Ppad < 3LL * K * G) return DCNV4B200_ERR_PADDED_DIM;
+  int tpg, chunks;
+  if (int rc = split_channels(D, dtype, &tpg, &chunks)) return rc;
+  const long long nq = (long long)N * Ho * Wo;
+  if (nq >= (1LL << 31) || (long long)H * W * G * D >= (1LL << 31) || (long long)G * D >= (1 << 24))
+    return DCNV4B200_ERR_TOO_LARGE;
+  const size_t bpq = (size_t)Ppad * elem_size(dtype) + (backward ? (size_t)Ppad * 4 : 0) +
+                     (softmax ? (size_t)G * 8 : 0);
+  if (bpq > (size_t)kStageBytesMax) return DCNV4B200_ERR_UNSUPPORTED;
+  p.N = N; p.H = H; p.W = W; p.G = G; p.D = D; p.C = G * D; p.Ho = Ho; p.Wo = Wo;
+  p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw; p.ph = ph; p.pw = pw; p.dh = dh; p.dw = dw;
+  p.K = K; p.Ppad = Ppad; p.remove_center = remove_center ? 1 : 0; p.softmax = softmax ? 1 : 0;
+  p.scale = offset_scale;
+  p.tpg = tpg; p.chunks = chunks; p.nq = (int)nq;
+  p.tile = pick_tile(nq, bpq, 1, G * tpg);
+  return 0;
+}
+
+int fill_fda(FdaParams& p, int dtype, int B, int Len_in, int G, int D, int L, int Len_q, int K, bool backward) {
+  if (!dtype_ok(dtype)) return DCNV4B200_ERR_DTYPE;
+  if (B <= 0 || Len_in <= 0 || G <= 0 || D <= 0 || L <= 0 || Len_q <= 0 || K <= 0) return DCNV4B200_ERR_SHAPE;
+  if (L > kMaxLevels) return DCNV4B200_ERR_UNSUPPORTED;
+  int tpg, chunks;
+  if (int rc = split_channels(D, dtype, &tpg, &chunks)) return rc;
+  const long long nq = (long long)B * Len_q;
+  if (nq >= (1LL << 31) || (long long)Len_in * G * D >= (1LL << 31) || (long long)G * D >= (1 << 24))
+    return DCNV4B200_ERR_TOO_LARGE;
+  const int es = elem_size(dtype);
+  const size_t row_bytes = (size_t)G * 3 * L * K * es;
+  // smallest number of queries whose rows span a multiple of 16 bytes
+  int unit = 1;
+  while ((row_bytes * unit) % 16 != 0) unit *= 2;
+  const size_t bpq = row_bytes + (backward ? (size_t)G * 3 * L * K * 4 : 0) + (size_t)G * 8;
+  if (bpq * unit + 64 > (size_t)kStageBytesMax) return DCNV4B200_ERR_UNSUPPORTED;
+  p.B = B; p.Len_in = Len_in; p.G = G; p.D = D; p.C = G * D; p.L = L; p.Len_q = Len_q; p.K = K; p.LK = L * K;
+  p.tpg = tpg; p.chunks = chunks; p.nq = (int)nq;
+  p.tile = pick_tile(nq, bpq, unit, G * tpg);
+  while ((size_t)p.tile * bpq + 64 > (size_t)kStageBytesMax && p.tile > unit) p.tile -= unit;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dcnv4b200_abi_version(void) { return DCNV4B200_ABI_VERSION; }
+
+const char* dcnv4b200_strerror(int code) {
+  switch (code) {
+    case DCNV4B200_OK: return "success";
+    case DCNV4B200_ERR_NULL: return "a required pointer is NULL";
+    case DCNV4B200_ERR_DTYPE: return "unknown dtype code (0 fp32, 1 fp16, 2 bf16)";
+    case DCNV4B200_ERR_SHAPE: return "non-positive or inconsistent dimension";
+    case DCNV4B200_ERR_ALIGN: return "pointer not 16-byte aligned";
+    case DCNV4B200_ERR_WORKSPACE: return "workspace missing or smaller than *_bwd_workspace_bytes()";
+    case DCNV4B200_ERR_UNSUPPORTED:
+      return "outside the supported parameter space (more than 8 levels, or one query's packed row "
+             "exceeds the 40 KiB staging budget)";
+    case DCNV4B200_ERR_PADDED_DIM: return "padded_offset_dim must be a multiple of 8 and >= 3*K*group";
+    case DCNV4B200_ERR_CHANNELS: return "group_channels must be a multiple of 4 (fp32) or 8 (fp16/bf16)";
+    case DCNV4B200_ERR_TOO_LARGE: return "tensor too large for 31-bit indexing";
+    default: break;
+  }
+  if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  return "unknown error code";
+}
+
+int dcnv4b200_out_size(int in, int pad, int dil, int k, int stride) {
+  if (stride <= 0) return 0;
+  const int span = in + 2 * pad - (dil * (k - 1) + 1);
+  if (span < 0) return 0;
+  return span / stride + 1;
+}
+
+int dcnv4b200_fwd(const void* value, const void* offset_mask, void* out, int dtype, int N, int H, int W,
+                  int G, int D, int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                  float offset_scale, int remove_center, int padded_offset_dim, int softmax, void* stream) {
+  if (!value || !offset_mask || !out) return DCNV4B200_ERR_NULL;
+  if (!aligned16(value) || !aligned16(offset_mask) || !aligned16(out)) return DCNV4B200_ERR_ALIGN;
+  DcnParams p;
+  if (int rc = fill_dcn(p, dtype, N, H, W, G, D, kh, kw, sh, sw, ph, pw, dh, dw, offset_scale, remove_center,
+                        padded_offset_dim, softmax, false))
+    return rc;
+  int* status = nullptr;
+  if (int rc = status_ptr(&status)) return rc;
+  return (int)launch_dcnv4_fwd(dtype, value, offset_mask, out, p, status, static_cast<cudaStream_t>(stream));
+}
+
+size_t dcnv4b200_bwd_workspace_bytes(int dtype, int N, int H, int W, int G, int D) {
+  if (dtype == DCNV4B200_F32 || !dtype_ok(dtype) || N <= 0 || H <= 0 || W <= 0 || G <= 0 || D <= 0) return 0;
+  return (size_t)N * H * W * G * D * sizeof(float);
+}
+
+int dcnv4b200_bwd(const void* value, const void* offset_mask, const void* grad_out, void* grad_value,
+                  void* grad_offset_mask, void* workspace, size_t workspace_bytes, int dtype, int N, int H,
+                  int W, int G, int D, int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                  float offset_scale, int remove_center, int padded_offset_dim, int softmax, void* stream) {
+  if (!value || !offset_mask || !grad_out || !grad_value || !grad_offset_mask) return DCNV4B200_ERR_NULL;
+  if (!aligned16(value) || !aligned16(offset_mask) || !aligned16(grad_out) || !aligned16(grad_value) ||
+      !aligned16(grad_offset_mask) || !aligned16(workspace))
+    return DCNV4B200_ERR_ALIGN;
+  DcnParams p;
+  if (int rc = fill_dcn(p, dtype, N, H, W, G, D, kh, kw, sh, sw, ph, pw, dh, dw, offset_scale, remove_center,
+                        padded_offset_dim, softmax, true))
+    return rc;
+  const size_t need = dcnv4b200_bwd_workspace_bytes(dtype, N, H, W, G, D);
+  if (need && (!workspace || workspace_bytes < need)) return DCNV4B200_ERR_WORKSPACE;
+  int* status = nullptr;
+  if (int rc = status_ptr(&status)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t n = (size_t)N * H * W * G * D;
+  float* acc = need ? static_cast<float*>(workspace) : static_cast<float*>(grad_value);
+  cudaError_t e = cudaMemsetAsync(acc, 0, n * sizeof(float), s);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_dcnv4_bwd(dtype, value, offset_mask, grad_out, acc, grad_offset_mask, p, status, s);
+  if (e != cudaSuccess) return (int)e;
+  if (need) e = launch_convert_f32(dtype, acc, grad_value, n, s);
+  return (int)e;
+}
+
+int fdab200_fwd(const void* value, const int64_t* spatial_shapes, const int64_t* level_start_index,
+                const void* sampling_loc_attn, void* out, int dtype, int B, int Len_in, int G, int D, int L,
+                int Len_q, int K, void* stream) {
+  if (!value || !spatial_shapes || !level_start_index || !sampling_loc_attn || !out) return DCNV4B200_ERR_NULL;
+  if (!aligned16(value) || !aligned16(sampling_loc_attn) || !aligned16(out)) return DCNV4B200_ERR_ALIGN;
+  FdaParams p;
+  if (int rc = fill_fda(p, dtype, B, Len_in, G, D, L, Len_q, K, false)) return rc;
+  int* status = nullptr;
+  if (int rc = status_ptr(&status)) return rc;
+  return (int)launch_fda_fwd(dtype, value, spatial_shapes, level_start_index, sampling_loc_attn, out, p, status,
+                             static_cast<cudaStream_t>(stream));
+}
+
+size_t fdab200_bwd_workspace_bytes(int dtype, int B, int Len_in, int G, int D) {
+  if (dtype == DCNV4B200_F32 || !dtype_ok(dtype) || B <= 0 || Len_in <= 0 || G <= 0 || D <= 0) return 0;
+  return (size_t)B * Len_in * G * D * sizeof(float);
+}
+
+int fdab200_bwd(const void* value, const int64_t* spatial_shapes, const int64_t* level_start_index,
+                const void* sampling_loc_attn, const void* grad_out, void* grad_value,
+                void* grad_sampling_loc_attn, void* workspace, size_t workspace_bytes, int dtype, int B,
+                int Len_in, int G, int D, int L, int Len_q, int K, void* stream) {
+  if (!value || !spatial_shapes || !level_start_index || !sampling_loc_attn || !grad_out || !grad_value ||
+      !grad_sampling_loc_attn)
+    return DCNV4B200_ERR_NULL;
+  if (!aligned16(value) || !aligned16(sampling_loc_attn) || !aligned16(grad_out) || !aligned16(grad_value) ||
+      !aligned16(grad_sampling_loc_attn) || !aligned16(workspace))
+    return DCNV4B200_ERR_ALIGN;
+  FdaParams p;
+  if (int rc = fill_fda(p, dtype, B, Len_in, G, D, L, Len_q, K, true)) return rc;
+  const size_t need = fdab200_bwd_workspace_bytes(dtype, B, Len_in, G, D);
+  if (need && (!workspace || workspace_bytes < need)) return DCNV4B200_ERR_WORKSPACE;
+  int* status = nullptr;
+  if (int rc = status_ptr(&status)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t n = (size_t)B * Len_in * G * D;
+  float* acc = need ? static_cast<float*>(workspace) : static_cast<float*>(grad_value);
+  cudaError_t e = cudaMemsetAsync(acc, 0, n * sizeof(float), s);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_fda_bwd(dtype, value, spatial_shapes, level_start_index, sampling_loc_attn, grad_out, acc,
+                     grad_sampling_loc_attn, p, status, s);
+  if (e != cudaSuccess) return (int)e;
+  if (need) e = launch_convert_f32(dtype, acc, grad_value, n, s);
+  return (int)e;
+}
+
+int dcnv4b200_fwd_corners(const void* offset_mask, int32_t* corners, int dtype, int N, int H, int W, int G,
+                          int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw, float offset_scale,
+                          int remove_center, int padded_offset_dim, void* stream) {
+  if (!offset_mask || !corners) return DCNV4B200_ERR_NULL;
+  DcnParams p;
+  const int D = vec_len(dtype);  // channel count is irrelevant to the coordinates
+  if (int rc = fill_dcn(p, dtype, N, H, W, G, D, kh, kw, sh, sw, ph, pw, dh, dw, offset_scale, remove_center,
+                        padded_offset_dim, 0, false))
+    return rc;
+  return (int)launch_dcnv4_corners(dtype, offset_mask, corners, p, static_cast<cudaStream_t>(stream));
+}
+
+int fdab200_fwd_corners(const int64_t* spatial_shapes, const void* sampling_loc_attn, int32_t* corners,
+                        int dtype, int B, int G, int L, int Len_q, int K, void* stream) {
+  if (!spatial_shapes || !sampling_loc_attn || !corners) return DCNV4B200_ERR_NULL;
+  FdaParams p;
+  if (int rc = fill_fda(p, dtype, B, 1, G, vec_len(dtype), L, Len_q, K, false)) return rc;
+  return (int)launch_fda_corners(dtype, spatial_shapes, sampling_loc_attn, corners, p,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int dcnv4b200_device_status(int* status_out) {
+  if (!status_out) return DCNV4B200_ERR_NULL;
+  int* status = nullptr;
+  if (int rc = status_ptr(&status)) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemcpy(status_out, status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return (int)e;
+  const int zero = 0;
+  e = cudaMemcpy(status, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  return (int)e;
+}
+
+}  // extern "C"

@@ -1,0 +1,33 @@
+"""`FlashDeformAttnFunction`: autograd glue with the reference's argument list
+(DCNv4_op/DCNv4/functions/flash_deform_attn_func.py:69-114).
+
+The reference refuses to import on compute capability 10.0 (its shared-memory table stops
+at 9.0, flash_deform_attn_func.py:21-36); this module has no such gate.
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+from torch.autograd.function import once_differentiable
+
+from .. import ops
+
+
+class FlashDeformAttnFunction(Function):
+    @staticmethod
+    def forward(ctx, value, value_spatial_shapes, value_level_start_index, sampling_loc_attn,
+                im2col_step, K=8):
+        ctx.im2col_step = im2col_step
+        ctx.K = K
+        output = ops.flash_deform_attn_forward(value, value_spatial_shapes, value_level_start_index,
+                                               sampling_loc_attn, im2col_step, K)
+        ctx.save_for_backward(value, value_spatial_shapes, value_level_start_index, sampling_loc_attn)
+        return output
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        value, shapes, starts, sampling_loc_attn = ctx.saved_tensors
+        grad_value, grad_sla = ops.flash_deform_attn_backward(
+            value, shapes, starts, sampling_loc_attn, grad_output.contiguous(), ctx.im2col_step, ctx.K)
+        return grad_value, None, None, grad_sla, None, None

@@ -1,0 +1,206 @@
+"""Tensor-level entry points over the C ABI (the role of the reference's `DCNv4.ext` module,
+DCNv4_op/src/vision.cpp:14-21): validate torch tensors the way the reference host wrappers
+do (DCNv4_op/src/cuda/dcnv4_cuda.cu:26-60, DCNv4_op/src/cuda/flash_deform_attn_cuda.cu:26-58),
+allocate outputs with torch (device memory and streams are torch's job here, nothing else),
+and call the library on the current CUDA stream.
+"""
+from __future__ import annotations
+
+from typing import List, Tuple
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"dcnv4_b200 supports float32/float16/bfloat16 tensors, got {t.dtype}") from None
+
+
+def _check_tensor(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} tensor has to be contiguous")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _check_step(batch: int, im2col_step: int) -> None:
+    step = min(batch, int(im2col_step))
+    if step <= 0 or batch % step != 0:
+        raise RuntimeError(f"batch({batch}) must divide im2col_step({step})")
+
+
+def dcnv4_forward(value, p_offset, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w,
+                  dilation_h, dilation_w, group, group_channels, offset_scale, im2col_step,
+                  remove_center, d_stride=None, block_thread=None, softmax=False) -> torch.Tensor:
+    """Positional signature of the reference's `ext.dcnv4_forward` (DCNv4_op/src/dcnv4.h:64-83).
+    `im2col_step` is validated like the reference does and otherwise unused (the whole batch
+    is one launch); `d_stride` / `block_thread` are accepted and ignored."""
+    _check_tensor(value, "input")
+    _check_tensor(p_offset, "offset")
+    if value.dim() != 4 or p_offset.dim() != 4:
+        raise RuntimeError("input and offset_mask must be (N,H,W,C) and (N,Ho,Wo,P) tensors")
+    if p_offset.dtype != value.dtype:
+        raise RuntimeError("input and offset_mask must have the same dtype")
+    N, H, W, C = value.shape
+    if C != group * group_channels:
+        raise RuntimeError(
+            f"Input channels and group times group channels wont match: ({C} vs {group * group_channels}).")
+    _check_step(N, im2col_step)
+    L = _lib.lib()
+    Ho = L.dcnv4b200_out_size(H, pad_h, dilation_h, kernel_h, stride_h)
+    Wo = L.dcnv4b200_out_size(W, pad_w, dilation_w, kernel_w, stride_w)
+    if tuple(p_offset.shape[:3]) != (N, Ho, Wo):
+        raise RuntimeError(f"offset_mask must be (N,{Ho},{Wo},P), got {tuple(p_offset.shape)}")
+    out = torch.empty((N, Ho, Wo, C), dtype=value.dtype, device=value.device)
+    with torch.cuda.device(value.device):
+        rc = L.dcnv4b200_fwd(value.data_ptr(), p_offset.data_ptr(), out.data_ptr(), _code(value),
+                             N, H, W, group, group_channels, kernel_h, kernel_w, stride_h, stride_w,
+                             pad_h, pad_w, dilation_h, dilation_w, float(offset_scale),
+                             int(remove_center), p_offset.shape[3], int(bool(softmax)), _stream(value))
+    _lib.check(rc, "dcnv4_forward")
+    return out
+
+
+def dcnv4_backward(value, p_offset, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w,
+                   dilation_h, dilation_w, group, group_channels, offset_scale, im2col_step,
+                   grad_output, remove_center, d_stride=None, block_thread=None,
+                   softmax=False) -> List[torch.Tensor]:
+    """Positional signature of `ext.dcnv4_backward` (DCNv4_op/src/dcnv4.h:85-107).  Returns
+    [grad_input, grad_offset_mask] in the dtype of `value` (bf16 included; the reference
+    raises a type error for bf16, DCNv4_op/src/cuda/dcnv4_cuda.cu:133-139,161)."""
+    _check_tensor(value, "input")
+    _check_tensor(p_offset, "offset")
+    _check_tensor(grad_output, "grad_output")
+    if p_offset.dtype != value.dtype or grad_output.dtype != value.dtype:
+        raise RuntimeError("input, offset_mask and grad_output must have the same dtype")
+    N, H, W, C = value.shape
+    if C != group * group_channels:
+        raise RuntimeError(
+            f"Input channels and group times group channels wont match: ({C} vs {group * group_channels}).")
+    _check_step(N, im2col_step)
+    L = _lib.lib()
+    Ho = L.dcnv4b200_out_size(H, pad_h, dilation_h, kernel_h, stride_h)
+    Wo = L.dcnv4b200_out_size(W, pad_w, dilation_w, kernel_w, stride_w)
+    if grad_output.numel() != N * Ho * Wo * C or tuple(p_offset.shape[:3]) != (N, Ho, Wo):
+        raise RuntimeError("grad_output / offset_mask shape does not match the output size")
+    code = _code(value)
+    grad_input = torch.empty_like(value)
+    grad_offset = torch.empty_like(p_offset)
+    ws_bytes = L.dcnv4b200_bwd_workspace_bytes(code, N, H, W, group, group_channels)
+    ws = torch.empty(ws_bytes // 4, dtype=torch.float32, device=value.device) if ws_bytes else None
+    with torch.cuda.device(value.device):
+        rc = L.dcnv4b200_bwd(value.data_ptr(), p_offset.data_ptr(), grad_output.data_ptr(),
+                             grad_input.data_ptr(), grad_offset.data_ptr(),
+                             ws.data_ptr() if ws is not None else None, ws_bytes, code,
+                             N, H, W, group, group_channels, kernel_h, kernel_w, stride_h, stride_w,
+                             pad_h, pad_w, dilation_h, dilation_w, float(offset_scale),
+                             int(remove_center), p_offset.shape[3], int(bool(softmax)), _stream(value))
+    _lib.check(rc, "dcnv4_backward")
+    return [grad_input, grad_offset]
+
+
+def _check_fda(value, spatial_shapes, level_start_index, sampling_loc_attn, K) -> Tuple[int, ...]:
+    _check_tensor(value, "value")
+    _check_tensor(spatial_shapes, "spatial_shapes")
+    _check_tensor(level_start_index, "level_start_index")
+    _check_tensor(sampling_loc_attn, "sampling_loc_attn")
+    if spatial_shapes.dtype != torch.int64 or level_start_index.dtype != torch.int64:
+        raise RuntimeError("spatial_shapes and level_start_index must be int64 tensors")
+    if value.dim() != 4 or sampling_loc_attn.dim() != 4:
+        raise RuntimeError("value must be (B,Len_in,G,D) and sampling_loc_attn (B,Len_q,G,3*L*K)")
+    if sampling_loc_attn.dtype != value.dtype:
+        raise RuntimeError("value and sampling_loc_attn must have the same dtype")
+    B, Len_in, G, D = value.shape
+    L = spatial_shapes.shape[0]
+    Len_q = sampling_loc_attn.shape[1]
+    if tuple(sampling_loc_attn.shape) != (B, Len_q, G, 3 * L * K):
+        raise RuntimeError(
+            f"sampling_loc_attn must be ({B},Len_q,{G},{3 * L * K}), got {tuple(sampling_loc_attn.shape)}")
+    return B, Len_in, G, D, L, Len_q
+
+
+def flash_deform_attn_forward(value, spatial_shapes, level_start_index, sampling_loc_attn,
+                              im2col_step=64, K=8, d_stride=None, block_thread=None) -> torch.Tensor:
+    """Positional signature of `ext.flash_deform_attn_forward` (DCNv4_op/src/dcnv4.h:19-38).
+    Returns (B, Len_q, G*D)."""
+    B, Len_in, G, D, L, Len_q = _check_fda(value, spatial_shapes, level_start_index, sampling_loc_attn, K)
+    _check_step(B, im2col_step)
+    out = torch.empty((B, Len_q, G * D), dtype=value.dtype, device=value.device)
+    with torch.cuda.device(value.device):
+        rc = _lib.lib().fdab200_fwd(value.data_ptr(), spatial_shapes.data_ptr(), level_start_index.data_ptr(),
+                                    sampling_loc_attn.data_ptr(), out.data_ptr(), _code(value),
+                                    B, Len_in, G, D, L, Len_q, K, _stream(value))
+    _lib.check(rc, "flash_deform_attn_forward")
+    return out
+
+
+def flash_deform_attn_backward(value, spatial_shapes, level_start_index, sampling_loc_attn, grad_output,
+                               im2col_step=64, K=8, d_stride=None, block_thread=None) -> List[torch.Tensor]:
+    """Positional signature of `ext.flash_deform_attn_backward` (DCNv4_op/src/dcnv4.h:40-62).
+    Returns [grad_value, grad_sampling_loc_attn] in the dtype of `value`."""
+    B, Len_in, G, D, L, Len_q = _check_fda(value, spatial_shapes, level_start_index, sampling_loc_attn, K)
+    _check_tensor(grad_output, "grad_output")
+    if grad_output.dtype != value.dtype or grad_output.numel() != B * Len_q * G * D:
+        raise RuntimeError("grad_output must be (B,Len_q,G*D) in the dtype of value")
+    _check_step(B, im2col_step)
+    lib = _lib.lib()
+    code = _code(value)
+    grad_value = torch.empty_like(value)
+    grad_sla = torch.empty_like(sampling_loc_attn)
+    ws_bytes = lib.fdab200_bwd_workspace_bytes(code, B, Len_in, G, D)
+    ws = torch.empty(ws_bytes // 4, dtype=torch.float32, device=value.device) if ws_bytes else None
+    with torch.cuda.device(value.device):
+        rc = lib.fdab200_bwd(value.data_ptr(), spatial_shapes.data_ptr(), level_start_index.data_ptr(),
+                             sampling_loc_attn.data_ptr(), grad_output.data_ptr(), grad_value.data_ptr(),
+                             grad_sla.data_ptr(), ws.data_ptr() if ws is not None else None, ws_bytes,
+                             code, B, Len_in, G, D, L, Len_q, K, _stream(value))
+    _lib.check(rc, "flash_deform_attn_backward")
+    return [grad_value, grad_sla]
+
+
+def dcnv4_corners(p_offset, H, W, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, dilation_h,
+                  dilation_w, group, offset_scale, remove_center) -> torch.Tensor:
+    """(N,Ho,Wo,G,K,2) int32 corner indices the kernels select (test aid)."""
+    _check_tensor(p_offset, "offset")
+    N, Ho, Wo, P = p_offset.shape
+    K = kernel_h * kernel_w - int(bool(remove_center))
+    corners = torch.empty((N, Ho, Wo, group, K, 2), dtype=torch.int32, device=p_offset.device)
+    with torch.cuda.device(p_offset.device):
+        rc = _lib.lib().dcnv4b200_fwd_corners(p_offset.data_ptr(), corners.data_ptr(), _code(p_offset),
+                                              N, H, W, group, kernel_h, kernel_w, stride_h, stride_w,
+                                              pad_h, pad_w, dilation_h, dilation_w, float(offset_scale),
+                                              int(remove_center), P, _stream(p_offset))
+    _lib.check(rc, "dcnv4_corners")
+    return corners
+
+
+def flash_deform_attn_corners(spatial_shapes, sampling_loc_attn, K) -> torch.Tensor:
+    """(B,Len_q,G,L*K,2) int32 corner indices the kernels select (test aid)."""
+    _check_tensor(sampling_loc_attn, "sampling_loc_attn")
+    B, Len_q, G, _ = sampling_loc_attn.shape
+    L = spatial_shapes.shape[0]
+    corners = torch.empty((B, Len_q, G, L * K, 2), dtype=torch.int32, device=sampling_loc_attn.device)
+    with torch.cuda.device(sampling_loc_attn.device):
+        rc = _lib.lib().fdab200_fwd_corners(spatial_shapes.data_ptr(), sampling_loc_attn.data_ptr(),
+                                            corners.data_ptr(), _code(sampling_loc_attn), B, G, L, Len_q, K,
+                                            _stream(sampling_loc_attn))
+    _lib.check(rc, "flash_deform_attn_corners")
+    return corners
+
+
+def device_status() -> int:
+    """Read-and-clear the current device's kernel status word (synchronises; test aid)."""
+    import ctypes as C
+    v = C.c_int(0)
+    _lib.check(_lib.lib().dcnv4b200_device_status(C.byref(v)), "device_status")
+    return v.value

@@ -1,0 +1,157 @@
+/*
+ * dcnv4_b200 -- C ABI of the B200 (sm_100a) DCNv4 / FlashDeformAttn operator library.
+ *
+ * This is the drop-in boundary: plain pointers and sizes, no framework types.  Each entry
+ * point names the reference interface it replaces (paths relative to the reference
+ * project root).  The reference exposes these four operations as the pybind module
+ * `DCNv4.ext` (DCNv4_op/src/vision.cpp:14-21, dispatch in DCNv4_op/src/dcnv4.h:19-107).
+ *
+ * Conventions
+ *  - Every pointer is DEVICE memory owned by the caller, 16-byte aligned, contiguous in the
+ *    layouts stated below.  The library never allocates, frees or synchronises; all work is
+ *    enqueued on `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream).
+ *  - Return value: 0 on success, a negative DCNV4B200_ERR_* for a rejected argument (nothing
+ *    was launched), or a positive cudaError_t reported by a launch.
+ *  - dtype: DCNV4B200_F32 / _F16 / _BF16 selects the storage type of all floating tensors of
+ *    a call; arithmetic is always fp32.
+ *  - The launch-tuning arguments of the reference (`d_stride`, `block_thread`) and its
+ *    `im2col_step` batch chunking have no counterpart: the kernels derive their own geometry
+ *    and take the whole batch in one launch.
+ */
+#ifndef DCNV4_B200_H_
+#define DCNV4_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DCNV4B200_ABI_VERSION 1
+
+enum { DCNV4B200_F32 = 0, DCNV4B200_F16 = 1, DCNV4B200_BF16 = 2 };
+
+enum {
+  DCNV4B200_OK = 0,
+  DCNV4B200_ERR_NULL = -1,        /* a required pointer is NULL */
+  DCNV4B200_ERR_DTYPE = -2,       /* unknown dtype code */
+  DCNV4B200_ERR_SHAPE = -3,       /* non-positive or inconsistent dimension */
+  DCNV4B200_ERR_ALIGN = -4,       /* pointer not 16-byte aligned */
+  DCNV4B200_ERR_WORKSPACE = -5,   /* workspace missing or too small */
+  DCNV4B200_ERR_UNSUPPORTED = -6, /* outside the supported parameter space (see strerror) */
+  DCNV4B200_ERR_PADDED_DIM = -7,  /* padded_offset_dim not a multiple of 8 or < 3*K*G */
+  DCNV4B200_ERR_CHANNELS = -8,    /* group_channels not a multiple of 16 bytes worth of elements */
+  DCNV4B200_ERR_TOO_LARGE = -9    /* an index would overflow 31 bits */
+};
+
+/* Version of this ABI (DCNV4B200_ABI_VERSION of the build). */
+int dcnv4b200_abi_version(void);
+
+/* Text for a return code of this library (negative codes) or of the CUDA runtime (positive). */
+const char* dcnv4b200_strerror(int code);
+
+/* Output extent along one axis: (in + 2*pad - (dil*(k-1)+1))/stride + 1.
+ * Replaces the size rule of DCNv4_op/src/cuda/dcnv4_cuda.cu:48-52. */
+int dcnv4b200_out_size(int in, int pad, int dil, int k, int stride);
+
+/*
+ * DCNv4 forward.  Replaces `dcnv4_forward` / `dcnv4_cuda_forward`
+ * (DCNv4_op/src/dcnv4.h:64-83, DCNv4_op/src/cuda/dcnv4_cuda.cu:26-90) and the kernel
+ * forward_kernel_dcn_reg (DCNv4_op/src/cuda/dcnv4_im2col_cuda.cuh:142-325).
+ *   value       (N,H,W,G*D)          channels-last
+ *   offset_mask (N,Ho,Wo,padded_offset_dim); per group g the 3K values at g*3K are
+ *               [x0,y0,...,x(K-1),y(K-1), m0..m(K-1)], K = kh*kw - remove_center, point order
+ *               k = i*kh + j with i over kernel_w (outer) and j over kernel_h (inner)
+ *   out         (N,Ho,Wo,G*D)        fully overwritten (no pre-zeroing needed)
+ * softmax != 0 normalises the K mask values per (query, group) before use.
+ */
+int dcnv4b200_fwd(const void* value, const void* offset_mask, void* out, int dtype,
+                  int N, int H, int W, int G, int D,
+                  int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                  float offset_scale, int remove_center, int padded_offset_dim, int softmax,
+                  void* stream);
+
+/* Bytes of caller-provided scratch `dcnv4b200_bwd` needs: 0 for fp32 (gradients accumulate
+ * in grad_value itself), N*H*W*G*D*4 for fp16/bf16 (the fp32 accumulation buffer that the
+ * reference allocates inside dcnv4_cuda_backward, DCNv4_op/src/cuda/dcnv4_cuda.cu:133-139). */
+size_t dcnv4b200_bwd_workspace_bytes(int dtype, int N, int H, int W, int G, int D);
+
+/*
+ * DCNv4 backward.  Replaces `dcnv4_backward` / `dcnv4_cuda_backward`
+ * (DCNv4_op/src/dcnv4.h:85-107, DCNv4_op/src/cuda/dcnv4_cuda.cu:92-175) and the kernels of
+ * DCNv4_op/src/cuda/dcnv4_col2im_cuda.cuh:20-472.
+ *   grad_out         (N,Ho,Wo,G*D)
+ *   grad_value       like value        fully overwritten
+ *   grad_offset_mask like offset_mask  fully overwritten, pad columns are zero
+ *   workspace        >= dcnv4b200_bwd_workspace_bytes(...) bytes (may be NULL when that is 0)
+ * grad_value is accumulated with floating-point atomics, so its low-order bits depend on
+ * the execution order; everything else is deterministic.
+ */
+int dcnv4b200_bwd(const void* value, const void* offset_mask, const void* grad_out,
+                  void* grad_value, void* grad_offset_mask, void* workspace, size_t workspace_bytes,
+                  int dtype, int N, int H, int W, int G, int D,
+                  int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                  float offset_scale, int remove_center, int padded_offset_dim, int softmax,
+                  void* stream);
+
+/*
+ * FlashDeformAttn forward.  Replaces `flash_deform_attn_forward` /
+ * `flash_deform_attn_cuda_forward` (DCNv4_op/src/dcnv4.h:19-38,
+ * DCNv4_op/src/cuda/flash_deform_attn_cuda.cu:26-84) and forward_kernel_reg
+ * (DCNv4_op/src/cuda/flash_deform_im2col_cuda.cuh:129-451).
+ *   value             (B,Len_in,G,D)
+ *   spatial_shapes    (L,2) int64 on the device: (H_l, W_l); the caller guarantees
+ *                     level_start[l] + H_l*W_l <= Len_in (the library cannot check device data)
+ *   level_start_index (L)   int64 on the device
+ *   sampling_loc_attn (B,Len_q,G,3*L*K): [x,y] for each of the L*K points (level-major,
+ *                     normalised to [0,1]) followed by the L*K attention logits
+ *   out               (B,Len_q,G*D)   fully overwritten
+ */
+int fdab200_fwd(const void* value, const int64_t* spatial_shapes, const int64_t* level_start_index,
+                const void* sampling_loc_attn, void* out, int dtype,
+                int B, int Len_in, int G, int D, int L, int Len_q, int K, void* stream);
+
+/* Scratch bytes for fdab200_bwd: 0 for fp32, B*Len_in*G*D*4 for fp16/bf16
+ * (DCNv4_op/src/cuda/flash_deform_attn_cuda.cu:125-131). */
+size_t fdab200_bwd_workspace_bytes(int dtype, int B, int Len_in, int G, int D);
+
+/*
+ * FlashDeformAttn backward.  Replaces `flash_deform_attn_backward` /
+ * `flash_deform_attn_cuda_backward` (DCNv4_op/src/dcnv4.h:40-62,
+ * DCNv4_op/src/cuda/flash_deform_attn_cuda.cu:86-163) and the kernels of
+ * DCNv4_op/src/cuda/flash_deform_col2im_cuda.cuh:20-580.
+ *   grad_out (B,Len_q,G*D); grad_value like value; grad_sampling_loc_attn like
+ *   sampling_loc_attn; both fully overwritten.
+ */
+int fdab200_bwd(const void* value, const int64_t* spatial_shapes, const int64_t* level_start_index,
+                const void* sampling_loc_attn, const void* grad_out,
+                void* grad_value, void* grad_sampling_loc_attn, void* workspace, size_t workspace_bytes,
+                int dtype, int B, int Len_in, int G, int D, int L, int Len_q, int K, void* stream);
+
+/*
+ * Corner-index probes: for every sampling point write (h_low, w_low) = floor of the fp32
+ * sampling coordinate the kernels use, or INT32_MIN twice for a point that fails the range
+ * test.  corners: (N,Ho,Wo,G,K,2) resp. (B,Len_q,G,L*K,2) int32.  They restate the
+ * coordinate arithmetic of DCNv4_op/src/cuda/dcnv4_im2col_cuda.cuh:203-227 and
+ * DCNv4_op/src/cuda/flash_deform_im2col_cuda.cuh:185-190 with DCNv4_op/src/cuda/common.h:47-48
+ * and exist so parity tests can check corner selection bit for bit.
+ */
+int dcnv4b200_fwd_corners(const void* offset_mask, int32_t* corners, int dtype,
+                          int N, int H, int W, int G,
+                          int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                          float offset_scale, int remove_center, int padded_offset_dim, void* stream);
+int fdab200_fwd_corners(const int64_t* spatial_shapes, const void* sampling_loc_attn, int32_t* corners,
+                        int dtype, int B, int G, int L, int Len_q, int K, void* stream);
+
+/*
+ * Read and clear the current device's kernel status word (0 = no kernel ever gave up on a
+ * bounded wait for its staged tile).  Synchronises the device; meant for tests and
+ * post-mortems, not for the hot path.  No counterpart in the reference.
+ */
+int dcnv4b200_device_status(int* status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DCNV4_B200_H_ */
