@@ -1,0 +1,378 @@
+#!/usr/bin/env python
+"""Benchmark of the DCNv4 operator hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload ("step"): one DCNv4 forward and one backward at each of the four FlashInternImage-T
+stage shapes (N=64 per GPU; (H=W, C, G) = (56,64,4), (28,128,8), (14,256,16), (7,512,32);
+group_channels 16, 3x3 / stride 1 / pad 1), in fp32 and in fp16: 16 operator calls.  All eight
+forwards run first, then all eight backwards, so the ~1 GB of distinct tensors a step touches
+passes through between two uses of any buffer (inputs larger than the 126 MB L2; no explicit
+flush).  Data is synthetic (seeded, the distributions the configuration states).
+
+`value` = algorithmic bytes of a step (each tensor counted once) x ranks / device time, inputs
+resident in HBM, calls made straight through the C ABI.  `e2e` = the same step through the public
+autograd API with pinned HOST buffers: host->device copies of every input and device->host
+copies of every result inside the timed region.  `roofline` describes the operator call that
+takes the most device time.  `cpu_baseline` times the grid_sample-based CPU formulation (the
+algorithm of the reference's pure-PyTorch core) on a bounded sample of the same workload.
+
+Multi-GPU (torchrun, one rank per GPU): the batch is sharded, every rank runs the same step on
+its own N=64 shard, there is no data-path collective; timing is barrier + synchronize on both
+sides, max over ranks (weak scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+STAGES = ((56, 64, 4), (28, 128, 8), (14, 256, 16), (7, 512, 32))
+N_PER_GPU = 64
+D = 16
+METRIC = "dcnv4_fwd_bwd_hbm_throughput"
+UNIT = "GB/s"
+WORKLOAD = "dcnv4_fwd+bwd sweep, FlashInternImage-T stage shapes, N=64/GPU, fp32+fp16"
+CPU_SAMPLE_N = 8
+
+
+def algorithmic_bytes(N, HW, C, G, es):
+    K = 9
+    Ppad = -(-3 * G * K // 8) * 8
+    fwd = es * (N * HW * HW * C + N * HW * HW * Ppad + N * HW * HW * C)
+    bwd = es * (2 * N * HW * HW * C + 2 * N * HW * HW * Ppad + N * HW * HW * C)
+    return fwd, bwd
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        rows = [r for ts, r in self.rows if t0 - 0.05 <= ts <= t1 + 0.15] or [r for _, r in self.rows]
+        for r in rows:
+            parts = [p.strip() for p in r.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+
+def cpu_pass(tensors):
+    from oracle import torch_core
+    for t, G in tensors:
+        torch_core.dcnv4_fwd_bwd(t["value"], t["offset_mask"], t["grad_out"],
+                                 3, 3, 1, 1, 1, 1, 1, 1, G, D, 1.0, 0)
+
+
+def cpu_baseline(reps=5, warm=2):
+    """grid_sample-based CPU formulation, fp32, forward + autograd backward, on a bounded sample:
+    the four stage shapes at N=CPU_SAMPLE_N.  Returns (GB/s, ms per pass, threads, description)."""
+    import torch
+    from oracle import inputs as oin
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    tensors, nbytes = [], 0
+    for HW, C, G in STAGES:
+        tensors.append((oin.dcnv4_inputs(CPU_SAMPLE_N, HW, HW, G, D, seed=HW), G))
+        f, b = algorithmic_bytes(CPU_SAMPLE_N, HW, C, G, 4)
+        nbytes += f + b
+    for _ in range(warm):
+        cpu_pass(tensors)
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        cpu_pass(tensors)
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    desc = (f"4 stage shapes at N={CPU_SAMPLE_N} (1/{N_PER_GPU // CPU_SAMPLE_N} of the batch), fp32 only, "
+            f"forward + autograd backward, median of {reps} passes")
+    return nbytes / med / 1e9, med * 1e3, torch.get_num_threads(), desc
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    gbs, ms, threads, desc = cpu_baseline(reps=max(1, args.steps), warm=max(1, min(args.warmup, 3)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": desc},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+def synthetic_inputs(torch, N, HW, G, seed, dtype, dev):
+    """value ~N(0,1); per group 18 offsets ~N(0,1) px then 9 masks ~U(0,1), pad columns zero;
+    grad_out ~N(0,1).  Seeded on the CPU generator, then cast and moved."""
+    g = torch.Generator().manual_seed(seed)
+    K, C = 9, G * D
+    Ppad = -(-3 * G * K // 8) * 8
+    value = torch.randn(N, HW, HW, C, generator=g)
+    off = torch.randn(N, HW, HW, G, 2 * K, generator=g)
+    msk = torch.rand(N, HW, HW, G, K, generator=g)
+    om = torch.zeros(N, HW, HW, Ppad)
+    om[..., : 3 * G * K] = torch.cat((off, msk), -1).reshape(N, HW, HW, 3 * G * K)
+    gout = torch.randn(N, HW, HW, C, generator=g)
+    return tuple(x.to(device=dev, dtype=dtype) for x in (value, om, gout))
+
+
+class Case:
+    """Device-resident tensors of one (stage, dtype) and its raw C-ABI calls."""
+
+    def __init__(self, torch, lib, HW, C, G, dtype, code, seed, dev):
+        self.HW, self.C, self.G, self.code, self.dtype = HW, C, G, code, dtype
+        self.value, self.om, self.gout = synthetic_inputs(torch, N_PER_GPU, HW, G, seed, dtype, dev)
+        self.out = torch.empty_like(self.value)
+        self.gvalue = torch.empty_like(self.value)
+        self.gom = torch.empty_like(self.om)
+        self.ws_bytes = lib.dcnv4b200_bwd_workspace_bytes(code, N_PER_GPU, HW, HW, G, D)
+        self.ws = torch.empty(max(self.ws_bytes, 16) // 4, dtype=torch.float32, device=dev)
+        es = self.value.element_size()
+        self.fwd_bytes, self.bwd_bytes = algorithmic_bytes(N_PER_GPU, HW, C, G, es)
+        self.lib = lib
+        self.name = f"{HW}x{HW}x{C}_{'fp32' if code == 0 else 'fp16'}"
+        self.scalars = (N_PER_GPU, HW, HW, G, D, 3, 3, 1, 1, 1, 1, 1, 1, 1.0, 0, self.om.shape[-1], 0)
+        self.kernels_fwd = 1
+        self.kernels_bwd = 1 + (1 if self.ws_bytes else 0)
+
+    def fwd(self, stream):
+        rc = self.lib.dcnv4b200_fwd(self.value.data_ptr(), self.om.data_ptr(), self.out.data_ptr(),
+                                    self.code, *self.scalars, stream)
+        assert rc == 0, rc
+
+    def bwd(self, stream):
+        rc = self.lib.dcnv4b200_bwd(self.value.data_ptr(), self.om.data_ptr(), self.gout.data_ptr(),
+                                    self.gvalue.data_ptr(), self.gom.data_ptr(),
+                                    self.ws.data_ptr() if self.ws_bytes else None, self.ws_bytes,
+                                    self.code, *self.scalars, stream)
+        assert rc == 0, rc
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from dcnv4_b200 import DCNv4Function, _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.lib()
+
+    cases = []
+    for si, (HW, C, G) in enumerate(STAGES):
+        for dtype, code in ((torch.float32, 0), (torch.float16, 1)):
+            cases.append(Case(torch, lib, HW, C, G, dtype, code, seed=1000 * rank + si, dev=dev))
+    step_bytes = sum(c.fwd_bytes + c.bwd_bytes for c in cases)
+    launches_per_step = sum(c.kernels_fwd + c.kernels_bwd for c in cases)
+    stream = torch.cuda.current_stream().cuda_stream
+    ops = [(c, "fwd") for c in cases] + [(c, "bwd") for c in cases]
+
+    def step(events=None):
+        for i, (c, which) in enumerate(ops):
+            if events is not None:
+                events[i][0].record()
+            (c.fwd if which == "fwd" else c.bwd)(stream)
+            if events is not None:
+                events[i][1].record()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in ops]
+          for _ in range(args.steps)]
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    wall0 = time.time()
+    t_start.record()
+    for k in range(args.steps):
+        step(ev[k])
+    t_end.record()
+    barrier()
+    wall1 = time.time()
+    elapsed_ms = t_start.elapsed_time(t_end)
+
+    # ---- end to end through the public autograd API with pinned host buffers
+    host_in, host_out = [], []
+    for c in cases:
+        host_in.append([x.cpu().pin_memory() for x in (c.value, c.om, c.gout)])
+        host_out.append([torch.empty_like(x, device="cpu").pin_memory() for x in (c.out, c.gvalue, c.gom)])
+    h2d = sum(x.numel() * x.element_size() for xs in host_in for x in xs)
+    d2h = sum(x.numel() * x.element_size() for xs in host_out for x in xs)
+
+    def e2e_step():
+        for c, hin, hout in zip(cases, host_in, host_out):
+            v = hin[0].to(dev, non_blocking=True).requires_grad_(True)
+            om = hin[1].to(dev, non_blocking=True).requires_grad_(True)
+            go = hin[2].to(dev, non_blocking=True)
+            out = DCNv4Function.apply(v, om, 3, 3, 1, 1, 1, 1, 1, 1, c.G, D, 1.0, 256, 0)
+            out.backward(go)
+            hout[0].copy_(out.detach(), non_blocking=True)
+            hout[1].copy_(v.grad, non_blocking=True)
+            hout[2].copy_(om.grad, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if rank == 0:
+        sampler.stop()
+
+    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = times.tolist()
+
+    if rank == 0:
+        per_op = []
+        for i, (c, which) in enumerate(ops):
+            ms = statistics.mean(ev[k][i][0].elapsed_time(ev[k][i][1]) for k in range(args.steps))
+            nbytes = c.fwd_bytes if which == "fwd" else c.bwd_bytes
+            per_op.append({"op": f"dcnv4_{which}_{c.name}", "ms": ms, "bytes": nbytes,
+                           "gbs": nbytes / ms / 1e6})
+        peak, peak_kind = peaks()
+        dom = max(per_op, key=lambda o: o["ms"])
+        for o in per_op:
+            o["frac"] = o["gbs"] / peak
+        value = step_bytes * world * args.steps / elapsed_ms / 1e6
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32+f16 storage, f32 arithmetic",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batch_per_gpu": N_PER_GPU, "global_batch": N_PER_GPU * world,
+                       "parallelism": f"batch-sharded x{world}, no collective",
+                       "l2": "inputs larger than L2: a step touches ~1 GB of distinct tensors between two "
+                             "uses of any buffer (all forwards, then all backwards); no explicit flush",
+                       "bytes_per_step_per_gpu": step_bytes},
+            "e2e": {"value": step_bytes * world * e2e_steps / e2e_ms / 1e6, "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "ms_per_step": e2e_ms / e2e_steps,
+                    "api": "dcnv4_b200.DCNv4Function.apply + backward, pinned host buffers"},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "kernel": dom["op"], "achieved": dom["gbs"], "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": None,
+                         "ms": dom["ms"], "algorithmic_bytes": dom["bytes"]},
+            "ops": per_op,
+            "clocks": sampler.summary(wall0, wall1),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            gbs, ms, threads, desc = cpu_baseline()
+            line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": desc, "ms_per_pass": ms}
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -162,7 +162,12 @@ def test_full_size_identity_and_linearity(shape, dtype):
     om2 = t["offset_mask"].clone()
     om2[..., : G * 27].view(N, HW, HW, G, 27)[..., 18:] *= 2.0
     out2 = ops.dcnv4_forward(t["value"], om2, *a[:-1], 256, a[-1])
-    assert torch.equal(out2, out1 * 2), "output must be exactly linear in the mask"
+    if dtype == torch.float32:
+        assert torch.equal(out2, out1 * 2), "output must be exactly linear in the mask"
+    else:  # results in fp16's subnormal range round on a fixed 2^-24 grid, so doubling is not exact there
+        normal = out1.abs() >= 2.0 ** -13
+        assert torch.equal(out2[normal], (out1 * 2)[normal])
+        assert (out2.float() - 2 * out1.float()).abs().max().item() <= 2.0 ** -23
 
 
 @pytest.mark.parametrize("shape", FULL, ids=lambda s: f"{s[0]}x{s[1]}x{s[2]}")
