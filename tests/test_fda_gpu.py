@@ -78,15 +78,15 @@ def test_full_size_properties(dtype):
     assert Len == 20197
     L = 4
     sla = t["sampling_loc_attn"].clone()
-    # every point -> centre of pixel (y=3, x=5) of its own level
-    for l, (H, W) in enumerate(oin.DETR_LEVELS):
-        sla[..., 2 * l * K: 2 * (l + 1) * K: 2] = (5 + 0.5) / W
-        sla[..., 2 * l * K + 1: 2 * (l + 1) * K: 2] = (3 + 0.5) / H
+    # every point -> centre of pixel (y=12, x=9) of level 0 (100x152): (9.5/152, 12.5/100) = (1/16, 1/8),
+    # both exactly representable in fp16, so the sample sits exactly on the pixel centre
+    sla[..., 0: 2 * L * K: 2] = 1.0 / 16
+    sla[..., 1: 2 * L * K: 2] = 1.0 / 8
     # logits: only level 0 matters (others pushed to -inf-ish)
     sla[..., 2 * L * K + K:] = -30000.0 if dtype == torch.float16 else -1e30
     from dcnv4_b200 import ops
     out = ops.flash_deform_attn_forward(t["value"], t["spatial_shapes"], t["level_start_index"], sla, 64, K)
-    expect = t["value"][:, 3 * 152 + 5].reshape(B, 1, G * D).expand(B, Len, G * D)
+    expect = t["value"][:, 12 * 152 + 9].reshape(B, 1, G * D).expand(B, Len, G * D)
     close(out, expect.double(), dict(rtol=2e-3 if dtype == torch.float16 else 1e-5, atol=1e-5), "pixel-centre sampling")
 
     if dtype == torch.float32:
