@@ -137,6 +137,9 @@ const char* dcnv4b200_strerror(int code) {
     case DCNV4B200_ERR_PADDED_DIM: return "padded_offset_dim must be a multiple of 8 and >= 3*K*group";
     case DCNV4B200_ERR_CHANNELS: return "group_channels must be a multiple of 4 (fp32) or 8 (fp16/bf16)";
     case DCNV4B200_ERR_TOO_LARGE: return "tensor too large for 31-bit indexing";
+    case DCNV4B200_ERR_SCRATCH_LIMIT:
+      return "N*H*W*G*D exceeds the built-in scratch of dcnv4b200_bwd_static_scratch "
+             "(see dcnv4b200_bwd_static_scratch_max_elements); use dcnv4b200_bwd with a workspace";
     default: break;
   }
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
@@ -273,6 +276,84 @@ int dcnv4b200_device_status(int* status_out) {
   if (e != cudaSuccess) return (int)e;
   const int zero = 0;
   e = cudaMemcpy(status, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  return (int)e;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Backward for callers that cannot allocate device memory.
+//
+// Some hosts of this library run the operator from inside an execution callback of a larger
+// runtime (an inference server's or a plugin framework's "enqueue" hook, a real-time loop)
+// where cudaMalloc is off limits: it synchronises the whole device, and it can simply fail
+// once the host application has handed all remaining device memory to its own arena.  Such a
+// caller can supply inputs and outputs, but has nowhere to get the fp32 accumulation buffer
+// that the 16-bit backward needs.  For them the buffer lives inside the library image.
+
+namespace {
+
+// fp32 accumulation scratch of the allocation-free backward.  Every GPU that loads this
+// library carries these 16 MiB until the process exits, whether the entry point is used or
+// not; that is why the limit is modest.
+constexpr size_t kStaticScratchFloats = size_t(4) << 20;  // 4 Mi floats = 16 MiB
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address.
+// The real address is looked up once per device, with that device current.
+float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+
+int static_scratch_ptr(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return DCNV4B200_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_static_scratch_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t dcnv4b200_bwd_static_scratch_max_elements(void) { return kStaticScratchFloats; }
+
+int dcnv4b200_bwd_static_scratch(const void* value, const void* offset_mask, const void* grad_out,
+                                 void* grad_value, void* grad_offset_mask, int dtype, int N, int H, int W,
+                                 int G, int D, int kh, int kw, int sh, int sw, int ph, int pw, int dh,
+                                 int dw, float offset_scale, int remove_center, int padded_offset_dim,
+                                 int softmax, void* stream) {
+  if (!value || !offset_mask || !grad_out || !grad_value || !grad_offset_mask) return DCNV4B200_ERR_NULL;
+  if (!aligned16(value) || !aligned16(offset_mask) || !aligned16(grad_out) || !aligned16(grad_value) ||
+      !aligned16(grad_offset_mask))
+    return DCNV4B200_ERR_ALIGN;
+  DcnParams p;
+  if (int rc = fill_dcn(p, dtype, N, H, W, G, D, kh, kw, sh, sw, ph, pw, dh, dw, offset_scale, remove_center,
+                        padded_offset_dim, softmax, true))
+    return rc;
+  const size_t n = (size_t)N * H * W * G * D;
+  const bool needs_scratch = dtype != DCNV4B200_F32;
+  if (needs_scratch && n > kStaticScratchFloats) return DCNV4B200_ERR_SCRATCH_LIMIT;
+  int* status = nullptr;
+  if (int rc = status_ptr(&status)) return rc;
+  float* acc = static_cast<float*>(grad_value);
+  if (needs_scratch) {
+    if (int rc = static_scratch_ptr(&acc)) return rc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The scratch keeps whatever the previous call left in it: clear the part this call sums into.
+  cudaError_t e = cudaMemsetAsync(acc, 0, n * sizeof(float), s);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_dcnv4_bwd(dtype, value, offset_mask, grad_out, acc, grad_offset_mask, p, status, s);
+  if (e != cudaSuccess) return (int)e;
+  if (needs_scratch) e = launch_convert_f32(dtype, acc, grad_value, n, s);
   return (int)e;
 }
 

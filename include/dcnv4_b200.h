@@ -42,7 +42,8 @@ enum {
   DCNV4B200_ERR_UNSUPPORTED = -6, /* outside the supported parameter space (see strerror) */
   DCNV4B200_ERR_PADDED_DIM = -7,  /* padded_offset_dim not a multiple of 8 or < 3*K*G */
   DCNV4B200_ERR_CHANNELS = -8,    /* group_channels not a multiple of 16 bytes worth of elements */
-  DCNV4B200_ERR_TOO_LARGE = -9    /* an index would overflow 31 bits */
+  DCNV4B200_ERR_TOO_LARGE = -9,   /* an index would overflow 31 bits */
+  DCNV4B200_ERR_SCRATCH_LIMIT = -10 /* tensor larger than the built-in scratch of *_static_scratch */
 };
 
 /* Version of this ABI (DCNV4B200_ABI_VERSION of the build). */
@@ -150,6 +151,41 @@ int fdab200_fwd_corners(const int64_t* spatial_shapes, const void* sampling_loc_
  * post-mortems, not for the hot path.  No counterpart in the reference.
  */
 int dcnv4b200_device_status(int* status_out);
+
+/*
+ * DCNv4 backward without any device allocation -- not even a caller-provided workspace.
+ * (This entry point has no counterpart in the reference, whose backward allocates its
+ * buffers with ATen on every call.)
+ *
+ * Who needs it: code that runs the operator from inside another runtime's execution hook
+ * (an inference server's or plugin framework's enqueue callback, a latency-critical loop).
+ * There cudaMalloc is forbidden -- it stalls the whole device and may fail outright once the
+ * host application has claimed the remaining memory for its own pools -- so the caller can
+ * pass inputs and outputs but cannot produce the fp32 accumulation buffer that
+ * dcnv4b200_bwd wants for fp16/bf16 tensors.  Here that buffer is a fixed array inside the
+ * library image instead.
+ *
+ * Same arguments and results as dcnv4b200_bwd minus workspace/workspace_bytes.  Limits and
+ * rules:
+ *  - fp16/bf16: N*H*W*G*D must not exceed dcnv4b200_bwd_static_scratch_max_elements()
+ *    (4 Mi elements = 16 MiB of fp32, held by every GPU that loads the library until the
+ *    process exits); larger tensors return DCNV4B200_ERR_SCRATCH_LIMIT and launch nothing.
+ *    fp32 tensors accumulate in grad_value itself and have no size limit.
+ *  - The first call on a device looks up the array's device address (one cheap runtime
+ *    query, no allocation); make that first call outside any stream capture.
+ *  - All calls on a device share the one array.  Each call clears the part it uses before
+ *    summing into it, so calls issued one after another on a stream are fine; calls that may
+ *    overlap on the GPU (different streams, different host threads) race on it and must be
+ *    serialised by the caller.
+ *  - Calls no cudaMalloc / cudaFree / allocating library routine.
+ */
+size_t dcnv4b200_bwd_static_scratch_max_elements(void);
+int dcnv4b200_bwd_static_scratch(const void* value, const void* offset_mask, const void* grad_out,
+                                 void* grad_value, void* grad_offset_mask,
+                                 int dtype, int N, int H, int W, int G, int D,
+                                 int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                 float offset_scale, int remove_center, int padded_offset_dim, int softmax,
+                                 void* stream);
 
 #ifdef __cplusplus
 }
