@@ -239,10 +239,15 @@ def run_ours(args):
     for si, (HW, C, G) in enumerate(STAGES):
         for dtype, code in ((torch.float32, 0), (torch.float16, 1)):
             cases.append(Case(torch, lib, HW, C, G, dtype, code, seed=1000 * rank + si, dev=dev))
-    step_bytes = sum(c.fwd_bytes + c.bwd_bytes for c in cases)
-    launches_per_step = sum(c.kernels_fwd + c.kernels_bwd for c in cases)
     stream = torch.cuda.current_stream().cuda_stream
     ops = [(c, "fwd") for c in cases] + [(c, "bwd") for c in cases]
+    if args.case:  # profiling aid: only the operator calls whose name contains the given text
+        ops = [(c, w) for c, w in ops if args.case in f"dcnv4_{w}_{c.name}"]
+        if not ops:
+            raise SystemExit(f"--case {args.case!r} matches no operator call")
+
+    step_bytes = sum(c.fwd_bytes if w == "fwd" else c.bwd_bytes for c, w in ops)
+    launches_per_step = sum(c.kernels_fwd if w == "fwd" else c.kernels_bwd for c, w in ops)
 
     def step(events=None):
         for i, (c, which) in enumerate(ops):
@@ -280,7 +285,7 @@ def run_ours(args):
 
     # ---- end to end through the public autograd API with pinned host buffers
     host_in, host_out = [], []
-    for c in cases:
+    for c in ([] if (args.no_e2e or args.case) else cases):
         host_in.append([x.cpu().pin_memory() for x in (c.value, c.om, c.gout)])
         host_out.append([torch.empty_like(x, device="cpu").pin_memory() for x in (c.out, c.gvalue, c.gom)])
     h2d = sum(x.numel() * x.element_size() for xs in host_in for x in xs)
@@ -298,16 +303,18 @@ def run_ours(args):
             hout[2].copy_(om.grad, non_blocking=True)
 
     e2e_steps = max(1, min(args.steps, 10))
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    e2e_ms = float("nan")
+    if not args.no_e2e and not args.case:
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
     if rank == 0:
         sampler.stop()
 
@@ -349,7 +356,9 @@ def run_ours(args):
             "ops": per_op,
             "clocks": sampler.summary(wall0, wall1),
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if args.case or args.no_e2e:
+            line["e2e"] = None
+        if world == 1 and not args.no_cpu_baseline and not args.case:
             gbs, ms, threads, desc = cpu_baseline()
             line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": desc, "ms_per_pass": ms}
@@ -368,6 +377,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end arm (profiling runs)")
+    ap.add_argument("--case", default="", help="profiling aid: run only operator calls whose name contains "
+                    "this text, e.g. fwd_56x56x64_fp32 (names are dcnv4_{fwd,bwd}_{HxWxC}_{fp32,fp16})")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
