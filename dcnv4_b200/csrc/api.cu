@@ -35,27 +35,66 @@ int status_ptr(int** out) {
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 inline int elem_size(int dtype) { return dtype == DCNV4B200_F32 ? 4 : 2; }
-inline int vec_len(int dtype) { return dtype == DCNV4B200_F32 ? 4 : 8; }
 inline bool dtype_ok(int dtype) { return dtype >= DCNV4B200_F32 && dtype <= DCNV4B200_BF16; }
 
-// D == vec * tpg * chunks with tpg the largest power of two (<= 32) dividing D/vec.
-int split_channels(int D, int dtype, int* tpg, int* chunks) {
-  const int v = vec_len(dtype);
-  if (D <= 0 || D % v != 0) return DCNV4B200_ERR_CHANNELS;
-  const int nvec = D / v;
+// D == per_lane * tpg * chunks with tpg the largest power of two (<= 32) dividing D/per_lane.
+void split_lanes(int D, int per_lane, int* tpg, int* chunks) {
+  const int nvec = D / per_lane;
   int t = 1;
   while (t < 32 && nvec % (t * 2) == 0) t *= 2;
   *tpg = t;
   *chunks = nvec / t;
+}
+
+// Lane geometry of a pair.  Forward lanes own 32 bytes of channels when the group's byte size
+// and the tensors' base addresses allow 256-bit accesses, else 16 bytes; backward lanes own
+// 4 channels.  D*elem must be a multiple of 16 bytes.
+int lane_geometry(int D, int dtype, bool wide_ok, int* vb, int* tpg, int* chunks, int* tpg_b, int* chunks_b) {
+  const int es = elem_size(dtype);
+  if (D <= 0 || (D * es) % 16 != 0) return DCNV4B200_ERR_CHANNELS;
+  *vb = (wide_ok && (D * es) % 32 == 0) ? 32 : 16;
+  split_lanes(D, *vb / es, tpg, chunks);
+  split_lanes(D, 4, tpg_b, chunks_b);
   return 0;
 }
 
-// Queries per CTA: as many as fit the staging budget, but never so many that the grid
-// drops below a few CTAs per SM; `unit` keeps every tile start 16-byte aligned.
+// 2-D query tile of one CTA for the DCNv4 kernels: at most `max_q` queries (what fits the
+// staging budget, capped so that a CTA keeps a few items per thread), as square as the
+// divisors of the output size allow, and small enough to leave a few CTAs per SM.
+void pick_tile_2d(int N, int Ho, int Wo, size_t bytes_per_query, int items_per_query, int* th, int* tw) {
+  long long max_q = (long long)(kStageBytesMax / bytes_per_query);
+  const long long cap_items = (6LL * kThreads + items_per_query - 1) / items_per_query;
+  if (max_q > cap_items) max_q = cap_items;
+  const long long cap_grid = (long long)N * Ho * Wo / (148LL * 4);
+  if (cap_grid >= 1 && max_q > cap_grid) max_q = cap_grid;
+  if (max_q < 1) max_q = 1;
+  // width: the divisor of Wo closest to sqrt(max_q) from below (ragged tiles are allowed, but
+  // exact ones waste no lanes); fall back to min(Wo, 8)
+  int best_w = 0;
+  for (int w = 1; w <= Wo && (long long)w * w <= max_q; ++w)
+    if (Wo % w == 0) best_w = w;
+  if (best_w < 4 && Wo >= 4) best_w = (int)(max_q < 8 ? max_q : 8) < Wo ? (int)(max_q < 8 ? max_q : 8) : Wo;
+  if (best_w < 1) best_w = 1;
+  long long h = max_q / best_w;
+  if (h < 1) h = 1;
+  if (h > Ho) h = Ho;
+  if (h > kMaxTileRows) h = kMaxTileRows;
+  int best_h = 1;
+  for (int t = 1; t <= h; ++t)
+    if (Ho % t == 0) best_h = t;
+  if (best_h * 2 <= h) best_h = (int)h;  // no useful divisor: accept a ragged last tile row
+  *th = best_h;
+  *tw = best_w;
+}
+
+// Queries per CTA of the 1-D tiles (FlashDeformAttn): as many as fit the staging budget, but
+// never so many that the grid drops below a few CTAs per SM; `unit` keeps every tile start
+// 16-byte aligned.
 int pick_tile(long long nq, size_t bytes_per_query, int unit, int items_per_query) {
   long long t = (long long)(kStageBytesMax / bytes_per_query);
-  const long long cap_items = (4LL * kThreads + items_per_query - 1) / items_per_query;  // ~4 items per thread
+  const long long cap_items = (6LL * kThreads + items_per_query - 1) / items_per_query;
   if (t > cap_items) t = cap_items;
   const long long cap_grid = nq / (148LL * 4);
   if (cap_grid >= 1 && t > cap_grid) t = cap_grid;
@@ -67,7 +106,7 @@ int pick_tile(long long nq, size_t bytes_per_query, int unit, int items_per_quer
 
 int fill_dcn(DcnParams& p, int dtype, int N, int H, int W, int G, int D, int kh, int kw, int sh, int sw,
              int ph, int pw, int dh, int dw, float offset_scale, int remove_center, int Ppad, int softmax,
-             bool backward) {
+             bool backward, bool wide_ok = false) {
   if (!dtype_ok(dtype)) return DCNV4B200_ERR_DTYPE;
   if (N <= 0 || H <= 0 || W <= 0 || G <= 0 || D <= 0 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 ||
       ph < 0 || pw < 0 || dh <= 0 || dw <= 0)
@@ -77,8 +116,7 @@ int fill_dcn(DcnParams& p, int dtype, int N, int H, int W, int G, int D, int kh,
   const int K = kh * kw - (remove_center ? 1 : 0);
   if (K <= 0) return DCNV4B200_ERR_SHAPE;
   if (Ppad % 8 != 0 || (long long)Ppad < 3LL * K * G) return DCNV4B200_ERR_PADDED_DIM;
-  int tpg, chunks;
-  if (int rc = split_channels(D, dtype, &tpg, &chunks)) return rc;
+  if (int rc = lane_geometry(D, dtype, wide_ok, &p.vb, &p.tpg, &p.chunks, &p.tpg_b, &p.chunks_b)) return rc;
   const long long nq = (long long)N * Ho * Wo;
   if (nq >= (1LL << 31) || (long long)H * W * G * D >= (1LL << 31) || (long long)G * D >= (1 << 24))
     return DCNV4B200_ERR_TOO_LARGE;
@@ -89,17 +127,20 @@ int fill_dcn(DcnParams& p, int dtype, int N, int H, int W, int G, int D, int kh,
   p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw; p.ph = ph; p.pw = pw; p.dh = dh; p.dw = dw;
   p.K = K; p.Ppad = Ppad; p.remove_center = remove_center ? 1 : 0; p.softmax = softmax ? 1 : 0;
   p.scale = offset_scale;
-  p.tpg = tpg; p.chunks = chunks; p.nq = (int)nq;
-  p.tile = pick_tile(nq, bpq, 1, G * tpg);
+  p.nq = (int)nq;
+  pick_tile_2d(N, Ho, Wo, bpq, G * (backward ? p.tpg_b : p.tpg), &p.th, &p.tw);
+  p.tiles_x = (Wo + p.tw - 1) / p.tw;
+  p.tiles_y = (Ho + p.th - 1) / p.th;
+  if ((long long)N * p.tiles_x * p.tiles_y >= (1LL << 31)) return DCNV4B200_ERR_TOO_LARGE;
   return 0;
 }
 
-int fill_fda(FdaParams& p, int dtype, int B, int Len_in, int G, int D, int L, int Len_q, int K, bool backward) {
+int fill_fda(FdaParams& p, int dtype, int B, int Len_in, int G, int D, int L, int Len_q, int K, bool backward,
+             bool wide_ok = false) {
   if (!dtype_ok(dtype)) return DCNV4B200_ERR_DTYPE;
   if (B <= 0 || Len_in <= 0 || G <= 0 || D <= 0 || L <= 0 || Len_q <= 0 || K <= 0) return DCNV4B200_ERR_SHAPE;
   if (L > kMaxLevels) return DCNV4B200_ERR_UNSUPPORTED;
-  int tpg, chunks;
-  if (int rc = split_channels(D, dtype, &tpg, &chunks)) return rc;
+  if (int rc = lane_geometry(D, dtype, wide_ok, &p.vb, &p.tpg, &p.chunks, &p.tpg_b, &p.chunks_b)) return rc;
   const long long nq = (long long)B * Len_q;
   if (nq >= (1LL << 31) || (long long)Len_in * G * D >= (1LL << 31) || (long long)G * D >= (1 << 24))
     return DCNV4B200_ERR_TOO_LARGE;
@@ -111,8 +152,8 @@ int fill_fda(FdaParams& p, int dtype, int B, int Len_in, int G, int D, int L, in
   const size_t bpq = row_bytes + (backward ? (size_t)G * 3 * L * K * 4 : 0) + (size_t)G * 8;
   if (bpq * unit + 64 > (size_t)kStageBytesMax) return DCNV4B200_ERR_UNSUPPORTED;
   p.B = B; p.Len_in = Len_in; p.G = G; p.D = D; p.C = G * D; p.L = L; p.Len_q = Len_q; p.K = K; p.LK = L * K;
-  p.tpg = tpg; p.chunks = chunks; p.nq = (int)nq;
-  p.tile = pick_tile(nq, bpq, unit, G * tpg);
+  p.nq = (int)nq;
+  p.tile = pick_tile(nq, bpq, unit, G * (backward ? p.tpg_b : p.tpg));
   while ((size_t)p.tile * bpq + 64 > (size_t)kStageBytesMax && p.tile > unit) p.tile -= unit;
   return 0;
 }
@@ -160,7 +201,7 @@ int dcnv4b200_fwd(const void* value, const void* offset_mask, void* out, int dty
   if (!aligned16(value) || !aligned16(offset_mask) || !aligned16(out)) return DCNV4B200_ERR_ALIGN;
   DcnParams p;
   if (int rc = fill_dcn(p, dtype, N, H, W, G, D, kh, kw, sh, sw, ph, pw, dh, dw, offset_scale, remove_center,
-                        padded_offset_dim, softmax, false))
+                        padded_offset_dim, softmax, false, aligned32(value) && aligned32(out)))
     return rc;
   int* status = nullptr;
   if (int rc = status_ptr(&status)) return rc;
@@ -205,7 +246,8 @@ int fdab200_fwd(const void* value, const int64_t* spatial_shapes, const int64_t*
   if (!value || !spatial_shapes || !level_start_index || !sampling_loc_attn || !out) return DCNV4B200_ERR_NULL;
   if (!aligned16(value) || !aligned16(sampling_loc_attn) || !aligned16(out)) return DCNV4B200_ERR_ALIGN;
   FdaParams p;
-  if (int rc = fill_fda(p, dtype, B, Len_in, G, D, L, Len_q, K, false)) return rc;
+  if (int rc = fill_fda(p, dtype, B, Len_in, G, D, L, Len_q, K, false, aligned32(value) && aligned32(out)))
+    return rc;
   int* status = nullptr;
   if (int rc = status_ptr(&status)) return rc;
   return (int)launch_fda_fwd(dtype, value, spatial_shapes, level_start_index, sampling_loc_attn, out, p, status,
@@ -250,7 +292,7 @@ int dcnv4b200_fwd_corners(const void* offset_mask, int32_t* corners, int dtype, 
                           int remove_center, int padded_offset_dim, void* stream) {
   if (!offset_mask || !corners) return DCNV4B200_ERR_NULL;
   DcnParams p;
-  const int D = vec_len(dtype);  // channel count is irrelevant to the coordinates
+  const int D = 16 / elem_size(dtype);  // channel count is irrelevant to the coordinates
   if (int rc = fill_dcn(p, dtype, N, H, W, G, D, kh, kw, sh, sw, ph, pw, dh, dw, offset_scale, remove_center,
                         padded_offset_dim, 0, false))
     return rc;
@@ -261,7 +303,7 @@ int fdab200_fwd_corners(const int64_t* spatial_shapes, const void* sampling_loc_
                         int dtype, int B, int G, int L, int Len_q, int K, void* stream) {
   if (!spatial_shapes || !sampling_loc_attn || !corners) return DCNV4B200_ERR_NULL;
   FdaParams p;
-  if (int rc = fill_fda(p, dtype, B, 1, G, vec_len(dtype), L, Len_q, K, false)) return rc;
+  if (int rc = fill_fda(p, dtype, B, 1, G, 16 / elem_size(dtype), L, Len_q, K, false)) return rc;
   return (int)launch_fda_corners(dtype, spatial_shapes, sampling_loc_attn, corners, p,
                                  static_cast<cudaStream_t>(stream));
 }

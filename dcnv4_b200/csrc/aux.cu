@@ -16,7 +16,9 @@ __global__ void convert_kernel(const float4* __restrict__ src, T* __restrict__ d
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
     const float4 a = src[2 * i], b = src[2 * i + 1];
     const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    reinterpret_cast<uint4*>(dst)[i] = pack(v, (const T*)nullptr);
+    uint32_t packed[4];
+    narrow(v, packed, (const T*)nullptr);
+    stg_raw(dst + i * 8, packed);
   }
   // ragged tail (n not a multiple of 8)
   if (blockIdx.x == 0) {
@@ -53,10 +55,10 @@ __global__ void dcnv4_corners_kernel(const T* __restrict__ om, int32_t* __restri
   const int ti = t / p.kh, tj = t % p.kh;
   const int cw = (p.dw * (p.kw - 1)) >> 1, ch = (p.dh * (p.kh - 1)) >> 1;
   const T* row = om + (size_t)q * p.Ppad + g * 3 * p.K;
-  const float w_im = dcn_coord(dcn_base(cw - p.pw + x * p.sw, cw, p.scale), ti * p.dw, to_f32(row[2 * k]), p.scale);
-  const float h_im = dcn_coord(dcn_base(ch - p.ph + y * p.sh, ch, p.scale), tj * p.dh, to_f32(row[2 * k + 1]), p.scale);
+  const float w_im = dcn_coord(dcn_base(cw - p.pw + x * p.sw, cw, p.scale), (float)(ti * p.dw), to_f32(row[2 * k]), p.scale);
+  const float h_im = dcn_coord(dcn_base(ch - p.ph + y * p.sh, ch, p.scale), (float)(tj * p.dh), to_f32(row[2 * k + 1]), p.scale);
   int h0 = kSkipped, w0 = kSkipped;
-  if (in_range(h_im, w_im, p.H, p.W)) {
+  if (in_range(h_im, w_im, (float)p.H, (float)p.W)) {
     const Footprint f = footprint(h_im, w_im, p.H, p.W);
     h0 = f.h0; w0 = f.w0;
   }
@@ -84,10 +86,10 @@ __global__ void fda_corners_kernel(const int64_t* __restrict__ shapes, const T* 
   const int l = t / p.K;
   const int Hl = (int)shapes[2 * l], Wl = (int)shapes[2 * l + 1];
   const T* row = sla + pr * 3 * p.LK;
-  const float w_im = fda_coord(to_f32(row[2 * t]), Wl);
-  const float h_im = fda_coord(to_f32(row[2 * t + 1]), Hl);
+  const float w_im = fda_coord(to_f32(row[2 * t]), (float)Wl);
+  const float h_im = fda_coord(to_f32(row[2 * t + 1]), (float)Hl);
   int h0 = kSkipped, w0 = kSkipped;
-  if (in_range(h_im, w_im, Hl, Wl)) {
+  if (in_range(h_im, w_im, (float)Hl, (float)Wl)) {
     const Footprint f = footprint(h_im, w_im, Hl, Wl);
     h0 = f.h0; w0 = f.w0;
   }

@@ -5,77 +5,91 @@
 // plus the zero-fills and the fp16 cast passes of the host wrapper
 // (DCNv4_op/src/cuda/dcnv4_cuda.cu:133-139,169-174).
 //
-//  * grad_value contributions go to an fp32 accumulation buffer with 16-byte vector
-//    reductions (red.global.add.v4.f32), one per corner and channel vector, instead of one
-//    scalar atomic per element.
+//  * A lane owns 4 channels of a pair.  Its grad_value contribution to a bilinear corner is
+//    one 16-byte vector reduction (red.global.add.v4.f32) into the fp32 accumulation buffer,
+//    and the D/4 lanes of a pair cover the corner's contiguous D*4 bytes in one instruction.
 //  * The three per-point partials (d/dx, d/dy, d/dmask) are reduced over the lanes of a pair
 //    with warp shuffles.  Lane 0 of the pair deposits them in a shared-memory image of the
 //    tile's grad_offset_mask rows; the CTA then writes whole rows (pad columns included, as
-//    zeros) with coalesced 16-byte stores, so grad_offset_mask needs no memset either.
+//    zeros) with coalesced 16-byte stores, so grad_offset_mask needs no memset.
+//  * Same 2-D query tiles and bulk-copy staging as the forward kernel.
 #include "common.cuh"
 
 namespace dcnb200 {
 
 size_t dcnv4_bwd_smem(const DcnParams& p, int elem) {
-  size_t b = 16 + (size_t)p.tile * p.Ppad * elem + (size_t)p.tile * p.Ppad * sizeof(float);
-  if (p.softmax) b += (size_t)p.tile * p.G * sizeof(float2);
+  size_t b = 16 + (size_t)p.th * p.tw * p.Ppad * elem + (size_t)p.th * p.tw * p.Ppad * sizeof(float);
+  if (p.softmax) b += (size_t)p.th * p.tw * p.G * sizeof(float2);
   return b;
 }
 
 template <typename T, int KH, int KW, bool ONE_CHUNK>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 dcnv4_bwd_kernel(const T* __restrict__ value, const T* __restrict__ om, const T* __restrict__ gout,
                  float* __restrict__ gvalue, T* __restrict__ gom, const DcnParams p, int* status) {
-  constexpr int V = Vec<T>::N;
+  constexpr int LB = 4 * (int)sizeof(T);  // bytes a lane loads per corner
+  constexpr int VS = 16 / (int)sizeof(T); // elements per 16-byte store of the write-out
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw);
   T* s_om = reinterpret_cast<T*>(smem_raw + 16);
-  float* s_g = reinterpret_cast<float*>(smem_raw + 16 + (size_t)p.tile * p.Ppad * sizeof(T));
-  float2* s_stat = reinterpret_cast<float2*>(s_g + (size_t)p.tile * p.Ppad);
+  float* s_g = reinterpret_cast<float*>(smem_raw + 16 + (size_t)p.th * p.tw * p.Ppad * sizeof(T));
+  float2* s_stat = reinterpret_cast<float2*>(s_g + (size_t)p.th * p.tw * p.Ppad);
 
-  const int q0 = blockIdx.x * p.tile;
-  const int nq_tile = min(p.tile, p.nq - q0);
-  if (!stage_span(s_om, om + (size_t)q0 * p.Ppad, (uint32_t)(nq_tile * p.Ppad * sizeof(T)), bar, status)) return;
+  const int tiles_per_img = p.tiles_x * p.tiles_y;
+  const int b = blockIdx.x / tiles_per_img;
+  const int t_in = blockIdx.x - b * tiles_per_img;
+  const int y0 = (t_in / p.tiles_x) * p.th, x0 = (t_in % p.tiles_x) * p.tw;
+  const int rows = min(p.th, p.Ho - y0), cols = min(p.tw, p.Wo - x0);
+  const size_t q_first = ((size_t)b * p.Ho + y0) * p.Wo + x0;
+  if (!stage_rows(s_om, om + q_first * p.Ppad, (uint32_t)(cols * p.Ppad * sizeof(T)), rows,
+                  (size_t)p.Wo * p.Ppad * sizeof(T), (uint32_t)(p.tw * p.Ppad * sizeof(T)), bar, status))
+    return;
 
   const int kh = KH ? KH : p.kh, kw = KW ? KW : p.kw;
   const int K = p.K;
   const int used = 3 * K * p.G;
+  const int n_q = p.th * p.tw;
 
   // pad columns of the gradient rows are zeros
-  for (int i = threadIdx.x; i < nq_tile * (p.Ppad - used); i += kThreads)
+  for (int i = threadIdx.x; i < n_q * (p.Ppad - used); i += kThreads)
     s_g[(i / (p.Ppad - used)) * p.Ppad + used + i % (p.Ppad - used)] = 0.f;
 
   if (p.softmax) {
-    for (int pr = threadIdx.x; pr < nq_tile * p.G; pr += kThreads) {
-      const T* row = s_om + (pr / p.G) * p.Ppad + (pr % p.G) * 3 * K + 2 * K;
-      float mx = -INFINITY;
-      for (int k = 0; k < K; ++k) mx = fmaxf(mx, to_f32(row[k]));
-      float sum = 0.f;
-      for (int k = 0; k < K; ++k) sum += __expf(to_f32(row[k]) - mx);
-      s_stat[pr] = make_float2(mx, 1.f / sum);
+    for (int pr = threadIdx.x; pr < n_q * p.G; pr += kThreads) {
+      const int ql = pr / p.G;
+      if (ql / p.tw < rows && ql % p.tw < cols) {
+        const T* row = s_om + ql * p.Ppad + (pr % p.G) * 3 * K + 2 * K;
+        float mx = -INFINITY;
+        for (int k = 0; k < K; ++k) mx = fmaxf(mx, to_f32(row[k]));
+        float sum = 0.f;
+        for (int k = 0; k < K; ++k) sum += __expf(to_f32(row[k]) - mx);
+        s_stat[pr] = make_float2(mx, 1.f / sum);
+      }
     }
     __syncthreads();
   }
 
   const int cw = (p.dw * (kw - 1)) >> 1, ch = (p.dh * (kh - 1)) >> 1;
   const int center = (kw / 2) * kh + (kh / 2);
-  const int QW = p.Ho * p.Wo;
-  const int n_items = nq_tile * p.G * p.tpg;
+  const int tpg = p.tpg_b;
+  const int n_items = n_q * p.G * tpg;
+  const size_t img_b = (size_t)b * p.H * p.W * p.C;
+  const float dwf = (float)p.dw, dhf = (float)p.dh;
 
   // Every lane of a warp takes part in the shuffles, so the loop runs over whole CTA-wide
-  // strides and lanes past the end work on item 0 with all memory traffic disabled.
+  // strides; lanes without a valid query work on query 0 with all memory traffic disabled.
   for (int base = 0; base < n_items; base += kThreads) {
-    const bool active = base + threadIdx.x < n_items;
-    const int item = active ? base + threadIdx.x : 0;
-    const int c = item % p.tpg;
-    const int pr = item / p.tpg;
+    const int item = base + threadIdx.x;
+    const int c = item % tpg;
+    const int pr_raw = item / tpg;
+    const int ql_raw = pr_raw / p.G;
+    const int ty_raw = ql_raw / p.tw, tx_raw = ql_raw - ty_raw * p.tw;
+    const bool active = item < n_items && ty_raw < rows && tx_raw < cols;
+    const int pr = active ? pr_raw : 0;
     const int g = pr % p.G;
     const int ql = pr / p.G;
-    const int q = q0 + ql;
-    const int b = q / QW;
-    const int rem = q - b * QW;
-    const int y = rem / p.Wo;
-    const int x = rem - y * p.Wo;
+    const int ty = ql / p.tw, tx = ql - ty * p.tw;
+    const int y = y0 + ty, x = x0 + tx;
 
     const T* row = s_om + ql * p.Ppad + g * 3 * K;
     float* grow = s_g + ql * p.Ppad + g * 3 * K;
@@ -84,10 +98,11 @@ dcnv4_bwd_kernel(const T* __restrict__ value, const T* __restrict__ om, const T*
     float2 stat = make_float2(0.f, 1.f);
     if (p.softmax) stat = s_stat[pr];
 
-    const size_t img_off = (size_t)b * p.H * p.W * p.C + g * p.D;
-    const T* go_ptr = gout + (size_t)q * p.C + g * p.D;
-    float gy0[V];
-    if (ONE_CHUNK) unpack(ldg_vec(go_ptr + c * V, active), gy0, (const T*)nullptr);
+    const T* img = value + img_b + g * p.D + c * 4;
+    float* gimg = gvalue + img_b + g * p.D + c * 4;
+    const T* go_ptr = gout + (((size_t)b * p.Ho + y) * p.Wo + x) * p.C + g * p.D + c * 4;
+    float gy0[4];
+    if (ONE_CHUNK) widen(ldg_raw<LB>(go_ptr, active).r, gy0, (const T*)nullptr);
 
     float soft_sum = 0.f;  // sum_k t_k (softmax backward), kept by lane 0 of the pair
 #pragma unroll
@@ -97,67 +112,33 @@ dcnv4_bwd_kernel(const T* __restrict__ value, const T* __restrict__ om, const T*
         const int t = i * kh + j;
         if (p.remove_center && t == center) continue;
         const int k = t - ((p.remove_center && t > center) ? 1 : 0);
-        const float w_im = dcn_coord(base_w, i * p.dw, to_f32(row[2 * k]), p.scale);
-        const float h_im = dcn_coord(base_h, j * p.dh, to_f32(row[2 * k + 1]), p.scale);
+        const float w_im = dcn_coord(base_w, (float)i * dwf, to_f32(row[2 * k]), p.scale);
+        const float h_im = dcn_coord(base_h, (float)j * dhf, to_f32(row[2 * k + 1]), p.scale);
         float m = to_f32(row[2 * K + k]);
         if (p.softmax) m = __expf(m - stat.x) * stat.y;
-        const bool ok = active && in_range(h_im, w_im, p.H, p.W);
-        const Footprint f = footprint(h_im, w_im, p.H, p.W);
-        const ptrdiff_t pix = ((ptrdiff_t)f.h0 * p.W + f.w0) * p.C;
-        const bool ok1 = ok && f.top && f.left, ok2 = ok && f.top && f.right;
-        const bool ok3 = ok && f.bot && f.left, ok4 = ok && f.bot && f.right;
-        const float w1 = f.hh * f.hw, w2 = f.hh * f.lw, w3 = f.lh * f.hw, w4 = f.lh * f.lw;
 
-        float d1 = 0.f, d2 = 0.f, d3 = 0.f, d4 = 0.f;  // sum_c gy_c * v_corner,c
-        const int n_chunks = ONE_CHUNK ? 1 : p.chunks;
-        for (int ci = 0; ci < n_chunks; ++ci) {
-          const int ch0 = (c + ci * p.tpg) * V;
-          float gy[V];
-          if (ONE_CHUNK) {
-#pragma unroll
-            for (int e = 0; e < V; ++e) gy[e] = gy0[e];
-          } else {
-            unpack(ldg_vec(go_ptr + ch0, active), gy, (const T*)nullptr);
-          }
-          const T* p1 = value + img_off + ch0 + pix;
-          const uint4 r1 = ldg_vec(p1, ok1);
-          const uint4 r2 = ldg_vec(p1 + p.C, ok2);
-          const uint4 r3 = ldg_vec(p1 + (size_t)p.W * p.C, ok3);
-          const uint4 r4 = ldg_vec(p1 + (size_t)p.W * p.C + p.C, ok4);
-          float* a1 = gvalue + img_off + ch0 + pix;
-          const float s1 = m * w1, s2 = m * w2, s3 = m * w3, s4 = m * w4;
-#pragma unroll
-          for (int e = 0; e < V; e += 4) {
-            if (ok1) red_add_v4(a1 + e, s1 * gy[e], s1 * gy[e + 1], s1 * gy[e + 2], s1 * gy[e + 3]);
-            if (ok2) red_add_v4(a1 + p.C + e, s2 * gy[e], s2 * gy[e + 1], s2 * gy[e + 2], s2 * gy[e + 3]);
-            if (ok3) red_add_v4(a1 + (size_t)p.W * p.C + e, s3 * gy[e], s3 * gy[e + 1], s3 * gy[e + 2], s3 * gy[e + 3]);
-            if (ok4) red_add_v4(a1 + (size_t)p.W * p.C + p.C + e, s4 * gy[e], s4 * gy[e + 1], s4 * gy[e + 2], s4 * gy[e + 3]);
-          }
-          float v1[V], v2[V], v3[V], v4[V];
-          unpack(r1, v1, (const T*)nullptr);
-          unpack(r2, v2, (const T*)nullptr);
-          unpack(r3, v3, (const T*)nullptr);
-          unpack(r4, v4, (const T*)nullptr);
-#pragma unroll
-          for (int e = 0; e < V; ++e) {
-            d1 = fmaf(gy[e], v1[e], d1);
-            d2 = fmaf(gy[e], v2[e], d2);
-            d3 = fmaf(gy[e], v3[e], d3);
-            d4 = fmaf(gy[e], v4[e], d4);
+        float gx = 0.f, gyv = 0.f, gm = 0.f;
+        bool ok;
+        if (ONE_CHUNK) {
+          ok = bwd_point<T>(img, gimg, p.H, p.W, p.C, h_im, w_im, m, active, gy0, gx, gyv, gm);
+        } else {
+          ok = false;
+          for (int ci = 0; ci < p.chunks_b; ++ci) {
+            const int off = ci * tpg * 4;
+            float gy[4];
+            widen(ldg_raw<LB>(go_ptr + off, active).r, gy, (const T*)nullptr);
+            ok = bwd_point<T>(img + off, gimg + off, p.H, p.W, p.C, h_im, w_im, m, active, gy, gx, gyv, gm);
           }
         }
-        // d/dw, d/dh of the bilinear value and the value itself, dotted with gy
-        float gx = f.hh * (d2 - d1) + f.lh * (d4 - d3);
-        float gyv = f.hw * (d3 - d1) + f.lw * (d4 - d2);
-        float gm = w1 * d1 + w2 * d2 + w3 * d3 + w4 * d4;
-        for (int o = p.tpg >> 1; o > 0; o >>= 1) {
+        for (int o = tpg >> 1; o > 0; o >>= 1) {
           gx += __shfl_xor_sync(0xffffffffu, gx, o);
           gyv += __shfl_xor_sync(0xffffffffu, gyv, o);
           gm += __shfl_xor_sync(0xffffffffu, gm, o);
         }
         if (active && c == 0) {
-          grow[2 * k] = ok ? p.scale * m * gx : 0.f;
-          grow[2 * k + 1] = ok ? p.scale * m * gyv : 0.f;
+          const float sm = p.scale * m;
+          grow[2 * k] = ok ? sm * gx : 0.f;
+          grow[2 * k + 1] = ok ? sm * gyv : 0.f;
           const float gmk = ok ? gm : 0.f;
           if (p.softmax) {
             grow[2 * K + k] = gmk * m;
@@ -177,27 +158,30 @@ dcnv4_bwd_kernel(const T* __restrict__ value, const T* __restrict__ om, const T*
   }
 
   __syncthreads();
-  // coalesced write-out of the tile's grad_offset_mask rows
-  const int n_vec = nq_tile * p.Ppad / V;
-  T* dst = gom + (size_t)q0 * p.Ppad;
-  for (int i = threadIdx.x; i < n_vec; i += kThreads) {
-    float v[V];
+  // coalesced write-out of the tile's grad_offset_mask rows (one contiguous span per tile row)
+  const int vec_per_row = cols * p.Ppad / VS;
+  for (int i = threadIdx.x; i < rows * vec_per_row; i += kThreads) {
+    const int r = i / vec_per_row, j = i - r * vec_per_row;
+    const float* src = s_g + (size_t)r * p.tw * p.Ppad + (size_t)j * VS;
+    float v[VS];
 #pragma unroll
-    for (int e = 0; e < V; e += 4) {
-      const float4 f4 = *reinterpret_cast<const float4*>(s_g + (size_t)i * V + e);
+    for (int e = 0; e < VS; e += 4) {
+      const float4 f4 = *reinterpret_cast<const float4*>(src + e);
       v[e] = f4.x; v[e + 1] = f4.y; v[e + 2] = f4.z; v[e + 3] = f4.w;
     }
-    *reinterpret_cast<uint4*>(dst + (size_t)i * V) = pack(v, (const T*)nullptr);
+    uint32_t packed[4];
+    narrow(v, packed, (const T*)nullptr);
+    stg_raw(gom + (q_first + (size_t)r * p.Wo) * p.Ppad + (size_t)j * VS, packed);
   }
 }
 
 template <typename T>
 static cudaError_t launch_t(const T* value, const T* om, const T* gout, float* gvalue, T* gom,
                             const DcnParams& p, int* status, cudaStream_t s) {
-  const int grid = (p.nq + p.tile - 1) / p.tile;
+  const int grid = p.N * p.tiles_x * p.tiles_y;
   const size_t smem = dcnv4_bwd_smem(p, sizeof(T));
   const bool k33 = p.kh == 3 && p.kw == 3;
-  if (k33 && p.chunks == 1)
+  if (k33 && p.chunks_b == 1)
     dcnv4_bwd_kernel<T, 3, 3, true><<<grid, kThreads, smem, s>>>(value, om, gout, gvalue, gom, p, status);
   else if (k33)
     dcnv4_bwd_kernel<T, 3, 3, false><<<grid, kThreads, smem, s>>>(value, om, gout, gvalue, gom, p, status);

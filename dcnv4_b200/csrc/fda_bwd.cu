@@ -5,7 +5,7 @@
 // (DCNv4_op/src/cuda/flash_deform_col2im_cuda.cuh:20-580) and the zero-fills / fp16 casts
 // of DCNv4_op/src/cuda/flash_deform_attn_cuda.cu:125-131,157-162.
 //
-// Same structure as the DCNv4 backward: vector reductions into an fp32 grad_value buffer,
+// Same structure as the DCNv4 backward (a lane owns 4 channels): vector reductions into an fp32 grad_value buffer,
 // shuffle reduction of the per-point partials over a pair's lanes, gradient rows assembled
 // in shared memory and written out whole.  The logit gradient uses
 //   grad_logit_i = p_i * (g_i - sum_j g_j p_j),
@@ -21,12 +21,13 @@ size_t fda_bwd_smem(const FdaParams& p, int elem) {
 }
 
 template <typename T, bool ONE_CHUNK>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 fda_bwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
                const int64_t* __restrict__ starts, const T* __restrict__ sla,
                const T* __restrict__ gout, float* __restrict__ gvalue, T* __restrict__ gsla,
                const FdaParams p, int* status) {
-  constexpr int V = Vec<T>::N;
+  constexpr int LB = 4 * (int)sizeof(T);   // bytes a lane loads per corner (4 channels)
+  constexpr int VS = 16 / (int)sizeof(T);  // elements per 16-byte store of the write-out
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int s_lvl[kMaxLevels * 3];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw);
@@ -44,7 +45,8 @@ fda_bwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
     s_lvl[threadIdx.x * 3 + 1] = (int)shapes[threadIdx.x * 2 + 1];
     s_lvl[threadIdx.x * 3 + 2] = (int)starts[threadIdx.x];
   }
-  if (!stage_span(s_row, sla + (size_t)q0 * rowlen, (uint32_t)(nq_tile * rowlen * sizeof(T)), bar, status)) return;
+  if (!stage_rows(s_row, sla + (size_t)q0 * rowlen, (uint32_t)(nq_tile * rowlen * sizeof(T)), 1, 0, 0, bar, status))
+    return;
 
   const int LK = p.LK;
   for (int pr = threadIdx.x; pr < nq_tile * p.G; pr += kThreads) {
@@ -57,12 +59,13 @@ fda_bwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
   }
   __syncthreads();
 
-  const int n_items = nq_tile * p.G * p.tpg;
+  const int tpg = p.tpg_b;
+  const int n_items = nq_tile * p.G * tpg;
   for (int base = 0; base < n_items; base += kThreads) {
     const bool active = base + threadIdx.x < n_items;
     const int item = active ? base + threadIdx.x : 0;
-    const int c = item % p.tpg;
-    const int pr = item / p.tpg;
+    const int c = item % tpg;
+    const int pr = item / tpg;
     const int g = pr % p.G;
     const int ql = pr / p.G;
     const int q = q0 + ql;
@@ -70,76 +73,43 @@ fda_bwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
     const T* row = s_row + pr * 3 * LK;
     float* grow = s_g + pr * 3 * LK;
     const float2 stat = s_stat[pr];
-    const T* go_ptr = gout + (size_t)q * p.C + g * p.D;
-    float gy0[V];
-    if (ONE_CHUNK) unpack(ldg_vec(go_ptr + c * V, active), gy0, (const T*)nullptr);
+    const T* go_ptr = gout + (size_t)q * p.C + g * p.D + c * 4;
+    float gy0[4];
+    if (ONE_CHUNK) widen(ldg_raw<LB>(go_ptr, active).r, gy0, (const T*)nullptr);
 
     float dot = 0.f;  // sum_t g_t p_t, kept by lane 0 of the pair
     for (int l = 0; l < p.L; ++l) {
       const int Hl = s_lvl[l * 3], Wl = s_lvl[l * 3 + 1];
-      const size_t img_off = ((size_t)b * p.Len_in + s_lvl[l * 3 + 2]) * p.C + g * p.D;
+      const float Hf = (float)Hl, Wf = (float)Wl;
+      const size_t img_off = ((size_t)b * p.Len_in + s_lvl[l * 3 + 2]) * p.C + g * p.D + c * 4;
 #pragma unroll 2
       for (int k = 0; k < p.K; ++k) {
         const int t = l * p.K + k;
-        const float w_im = fda_coord(to_f32(row[2 * t]), Wl);
-        const float h_im = fda_coord(to_f32(row[2 * t + 1]), Hl);
+        const float w_im = fda_coord(to_f32(row[2 * t]), Wf);
+        const float h_im = fda_coord(to_f32(row[2 * t + 1]), Hf);
         const float m = __expf(to_f32(row[2 * LK + t]) - stat.x) * stat.y;
-        const bool ok = active && in_range(h_im, w_im, Hl, Wl);
-        const Footprint f = footprint(h_im, w_im, Hl, Wl);
-        const ptrdiff_t pix = ((ptrdiff_t)f.h0 * Wl + f.w0) * p.C;
-        const bool ok1 = ok && f.top && f.left, ok2 = ok && f.top && f.right;
-        const bool ok3 = ok && f.bot && f.left, ok4 = ok && f.bot && f.right;
-        const float w1 = f.hh * f.hw, w2 = f.hh * f.lw, w3 = f.lh * f.hw, w4 = f.lh * f.lw;
-
-        float d1 = 0.f, d2 = 0.f, d3 = 0.f, d4 = 0.f;
-        const int n_chunks = ONE_CHUNK ? 1 : p.chunks;
-        for (int ci = 0; ci < n_chunks; ++ci) {
-          const int ch0 = (c + ci * p.tpg) * V;
-          float gy[V];
-          if (ONE_CHUNK) {
-#pragma unroll
-            for (int e = 0; e < V; ++e) gy[e] = gy0[e];
-          } else {
-            unpack(ldg_vec(go_ptr + ch0, active), gy, (const T*)nullptr);
-          }
-          const T* p1 = value + img_off + ch0 + pix;
-          const uint4 r1 = ldg_vec(p1, ok1);
-          const uint4 r2 = ldg_vec(p1 + p.C, ok2);
-          const uint4 r3 = ldg_vec(p1 + (size_t)Wl * p.C, ok3);
-          const uint4 r4 = ldg_vec(p1 + (size_t)Wl * p.C + p.C, ok4);
-          float* a1 = gvalue + img_off + ch0 + pix;
-          const float s1 = m * w1, s2 = m * w2, s3 = m * w3, s4 = m * w4;
-#pragma unroll
-          for (int e = 0; e < V; e += 4) {
-            if (ok1) red_add_v4(a1 + e, s1 * gy[e], s1 * gy[e + 1], s1 * gy[e + 2], s1 * gy[e + 3]);
-            if (ok2) red_add_v4(a1 + p.C + e, s2 * gy[e], s2 * gy[e + 1], s2 * gy[e + 2], s2 * gy[e + 3]);
-            if (ok3) red_add_v4(a1 + (size_t)Wl * p.C + e, s3 * gy[e], s3 * gy[e + 1], s3 * gy[e + 2], s3 * gy[e + 3]);
-            if (ok4) red_add_v4(a1 + (size_t)Wl * p.C + p.C + e, s4 * gy[e], s4 * gy[e + 1], s4 * gy[e + 2], s4 * gy[e + 3]);
-          }
-          float v1[V], v2[V], v3[V], v4[V];
-          unpack(r1, v1, (const T*)nullptr);
-          unpack(r2, v2, (const T*)nullptr);
-          unpack(r3, v3, (const T*)nullptr);
-          unpack(r4, v4, (const T*)nullptr);
-#pragma unroll
-          for (int e = 0; e < V; ++e) {
-            d1 = fmaf(gy[e], v1[e], d1);
-            d2 = fmaf(gy[e], v2[e], d2);
-            d3 = fmaf(gy[e], v3[e], d3);
-            d4 = fmaf(gy[e], v4[e], d4);
+        float gx = 0.f, gyv = 0.f, gm = 0.f;
+        bool ok;
+        if (ONE_CHUNK) {
+          ok = bwd_point<T>(value + img_off, gvalue + img_off, Hl, Wl, p.C, h_im, w_im, m, active, gy0, gx, gyv, gm);
+        } else {
+          ok = false;
+          for (int ci = 0; ci < p.chunks_b; ++ci) {
+            const int off = ci * tpg * 4;
+            float gy[4];
+            widen(ldg_raw<LB>(go_ptr + off, active).r, gy, (const T*)nullptr);
+            ok = bwd_point<T>(value + img_off + off, gvalue + img_off + off, Hl, Wl, p.C, h_im, w_im, m, active,
+                              gy, gx, gyv, gm);
           }
         }
-        float gx = f.hh * (d2 - d1) + f.lh * (d4 - d3);
-        float gyv = f.hw * (d3 - d1) + f.lw * (d4 - d2);
-        float gm = w1 * d1 + w2 * d2 + w3 * d3 + w4 * d4;
-        for (int o = p.tpg >> 1; o > 0; o >>= 1) {
+        for (int o = tpg >> 1; o > 0; o >>= 1) {
           gx += __shfl_xor_sync(0xffffffffu, gx, o);
           gyv += __shfl_xor_sync(0xffffffffu, gyv, o);
           gm += __shfl_xor_sync(0xffffffffu, gm, o);
         }
         if (active && c == 0) {
-          grow[2 * t] = ok ? (float)Wl * m * gx : 0.f;
-          grow[2 * t + 1] = ok ? (float)Hl * m * gyv : 0.f;
+          grow[2 * t] = ok ? Wf * m * gx : 0.f;
+          grow[2 * t + 1] = ok ? Hf * m * gyv : 0.f;
           const float gt = ok ? gm : 0.f;
           grow[2 * LK + t] = gt;
           dot = fmaf(gt, m, dot);
@@ -157,18 +127,20 @@ fda_bwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
   __syncthreads();
   // write the tile's gradient rows: 16-byte vectors, then a ragged tail element by element
   const int n_elem = nq_tile * rowlen;
-  const int n_vec = n_elem / V;
+  const int n_vec = n_elem / VS;
   T* dst = gsla + (size_t)q0 * rowlen;
   for (int i = threadIdx.x; i < n_vec; i += kThreads) {
-    float v[V];
+    float v[VS];
 #pragma unroll
-    for (int e = 0; e < V; e += 4) {
-      const float4 f4 = *reinterpret_cast<const float4*>(s_g + (size_t)i * V + e);
+    for (int e = 0; e < VS; e += 4) {
+      const float4 f4 = *reinterpret_cast<const float4*>(s_g + (size_t)i * VS + e);
       v[e] = f4.x; v[e + 1] = f4.y; v[e + 2] = f4.z; v[e + 3] = f4.w;
     }
-    *reinterpret_cast<uint4*>(dst + (size_t)i * V) = pack(v, (const T*)nullptr);
+    uint32_t packed[4];
+    narrow(v, packed, (const T*)nullptr);
+    stg_raw(dst + (size_t)i * VS, packed);
   }
-  for (int i = n_vec * V + threadIdx.x; i < n_elem; i += kThreads) dst[i] = from_f32<T>(s_g[i]);
+  for (int i = n_vec * VS + threadIdx.x; i < n_elem; i += kThreads) dst[i] = from_f32<T>(s_g[i]);
 }
 
 template <typename T>
@@ -177,7 +149,7 @@ static cudaError_t launch_t(const T* value, const int64_t* shapes, const int64_t
                             cudaStream_t s) {
   const int grid = (p.nq + p.tile - 1) / p.tile;
   const size_t smem = fda_bwd_smem(p, sizeof(T));
-  if (p.chunks == 1)
+  if (p.chunks_b == 1)
     fda_bwd_kernel<T, true><<<grid, kThreads, smem, s>>>(value, shapes, starts, sla, gout, gvalue, gsla, p, status);
   else
     fda_bwd_kernel<T, false><<<grid, kThreads, smem, s>>>(value, shapes, starts, sla, gout, gvalue, gsla, p, status);

@@ -5,7 +5,7 @@
 // (DCNv4_op/src/cuda/flash_deform_im2col_cuda.cuh:129-451) and the zero-filled output of
 // DCNv4_op/src/cuda/flash_deform_attn_cuda.cu:60.
 //
-// The softmax statistics (max, 1/sum) are computed once per (query, head) while the tile is
+// A lane owns 32 bytes of channels (one 256-bit load per corner).  The softmax statistics (max, 1/sum) are computed once per (query, head) while the tile is
 // in shared memory -- not once per channel lane -- and the level table (H_l, W_l, start_l)
 // is read from device memory once per CTA instead of once per thread and level.
 #include "common.cuh"
@@ -17,12 +17,12 @@ size_t fda_fwd_smem(const FdaParams& p, int elem) {
   return 16 + row + (size_t)p.tile * p.G * sizeof(float2);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kThreads)
+template <typename T, int VB>
+__global__ void __launch_bounds__(kThreads, 2)
 fda_fwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
                const int64_t* __restrict__ starts, const T* __restrict__ sla, T* __restrict__ out,
                const FdaParams p, int* status) {
-  constexpr int V = Vec<T>::N;
+  constexpr int V = VB / (int)sizeof(T);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int s_lvl[kMaxLevels * 3];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw);
@@ -38,7 +38,8 @@ fda_fwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
     s_lvl[threadIdx.x * 3 + 1] = (int)shapes[threadIdx.x * 2 + 1];
     s_lvl[threadIdx.x * 3 + 2] = (int)starts[threadIdx.x];
   }
-  if (!stage_span(s_row, sla + (size_t)q0 * rowlen, (uint32_t)(nq_tile * rowlen * sizeof(T)), bar, status)) return;
+  if (!stage_rows(s_row, sla + (size_t)q0 * rowlen, (uint32_t)(nq_tile * rowlen * sizeof(T)), 1, 0, 0, bar, status))
+    return;
 
   const int LK = p.LK;
   for (int pr = threadIdx.x; pr < nq_tile * p.G; pr += kThreads) {
@@ -69,32 +70,20 @@ fda_fwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
       for (int e = 0; e < V; ++e) acc[e] = 0.f;
       for (int l = 0; l < p.L; ++l) {
         const int Hl = s_lvl[l * 3], Wl = s_lvl[l * 3 + 1];
+        const float Hf = (float)Hl, Wf = (float)Wl;
         const T* img = value + ((size_t)b * p.Len_in + s_lvl[l * 3 + 2]) * p.C + g * p.D + ch0;
 #pragma unroll 4
         for (int k = 0; k < p.K; ++k) {
           const int t = l * p.K + k;
-          const float w_im = fda_coord(to_f32(row[2 * t]), Wl);
-          const float h_im = fda_coord(to_f32(row[2 * t + 1]), Hl);
+          const float w_im = fda_coord(to_f32(row[2 * t]), Wf);
+          const float h_im = fda_coord(to_f32(row[2 * t + 1]), Hf);
           const float m = __expf(to_f32(row[2 * LK + t]) - stat.x) * stat.y;
-          const bool ok = in_range(h_im, w_im, Hl, Wl);
-          const Footprint f = footprint(h_im, w_im, Hl, Wl);
-          const T* p1 = img + ((ptrdiff_t)f.h0 * Wl + f.w0) * p.C;
-          const uint4 r1 = ldg_vec(p1, ok && f.top && f.left);
-          const uint4 r2 = ldg_vec(p1 + p.C, ok && f.top && f.right);
-          const uint4 r3 = ldg_vec(p1 + (size_t)Wl * p.C, ok && f.bot && f.left);
-          const uint4 r4 = ldg_vec(p1 + (size_t)Wl * p.C + p.C, ok && f.bot && f.right);
-          const float w1 = m * f.hh * f.hw, w2 = m * f.hh * f.lw, w3 = m * f.lh * f.hw, w4 = m * f.lh * f.lw;
-          float v1[V], v2[V], v3[V], v4[V];
-          unpack(r1, v1, (const T*)nullptr);
-          unpack(r2, v2, (const T*)nullptr);
-          unpack(r3, v3, (const T*)nullptr);
-          unpack(r4, v4, (const T*)nullptr);
-#pragma unroll
-          for (int e = 0; e < V; ++e)
-            acc[e] = fmaf(w1, v1[e], fmaf(w2, v2[e], fmaf(w3, v3[e], fmaf(w4, v4[e], acc[e]))));
+          fwd_point<T, VB>(img, Hl, Wl, p.C, h_im, w_im, m, acc);
         }
       }
-      *reinterpret_cast<uint4*>(out + (size_t)q * p.C + g * p.D + ch0) = pack(acc, (const T*)nullptr);
+      uint32_t packed[VB / 4];
+      narrow(acc, packed, (const T*)nullptr);
+      stg_raw(out + (size_t)q * p.C + g * p.D + ch0, packed);
     }
   }
 }
@@ -103,7 +92,11 @@ template <typename T>
 static cudaError_t launch_t(const T* value, const int64_t* shapes, const int64_t* starts, const T* sla,
                             T* out, const FdaParams& p, int* status, cudaStream_t s) {
   const int grid = (p.nq + p.tile - 1) / p.tile;
-  fda_fwd_kernel<T><<<grid, kThreads, fda_fwd_smem(p, sizeof(T)), s>>>(value, shapes, starts, sla, out, p, status);
+  const size_t smem = fda_fwd_smem(p, sizeof(T));
+  if (p.vb == 32)
+    fda_fwd_kernel<T, 32><<<grid, kThreads, smem, s>>>(value, shapes, starts, sla, out, p, status);
+  else
+    fda_fwd_kernel<T, 16><<<grid, kThreads, smem, s>>>(value, shapes, starts, sla, out, p, status);
   return cudaGetLastError();
 }
 
