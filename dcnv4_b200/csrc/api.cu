@@ -17,8 +17,10 @@ __device__ int g_status_word;
 constexpr int kMaxDevices = 64;
 std::mutex g_mu;
 int* g_status_ptr[kMaxDevices] = {nullptr};
+int g_sm_count[kMaxDevices] = {0};
 
-int status_ptr(int** out) {
+// Status word address and SM count of the current device (looked up once per device).
+int status_ptr(int** out, int* sm_count = nullptr) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
@@ -28,9 +30,14 @@ int status_ptr(int** out) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_status_word);
     if (e != cudaSuccess) return (int)e;
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    g_sm_count[dev] = sms > 0 ? sms : 1;
     g_status_ptr[dev] = static_cast<int*>(p);
   }
   *out = g_status_ptr[dev];
+  if (sm_count) *sm_count = g_sm_count[dev];
   return 0;
 }
 
@@ -48,34 +55,60 @@ void split_lanes(int D, int per_lane, int* tpg, int* chunks) {
   *chunks = nvec / t;
 }
 
-// Lane geometry of a pair.  Forward lanes own 32 bytes of channels when the group's byte size
-// and the tensors' base addresses allow 256-bit accesses, else 16 bytes; backward lanes own
-// 4 channels.  D*elem must be a multiple of 16 bytes.
-int lane_geometry(int D, int dtype, bool wide_ok, int* vb, int* tpg, int* chunks, int* tpg_b, int* chunks_b) {
+FastDiv make_div(int d) {
+  FastDiv f;
+  f.d = (uint32_t)d;
+  f.mul = d > 1 ? (uint32_t)(0x100000000ULL / (uint64_t)d) + 1u : 0u;
+  return f;
+}
+
+// Lane geometry of a pair, chosen from measurements on B200 (random 64-byte gathers): the L1
+// serves about one distinct 128-byte line per cycle whatever the access width, so a
+// bilinear corner of a pair should be fetched by ONE load instruction -- lanes * vector bytes
+// == group bytes -- and a pair's vector reductions should likewise share one instruction.
+//  * forward lane: 32 bytes of channels (one 256-bit load per corner) when D*elem is a multiple
+//    of 32 and the tensors are 32-byte aligned, else 16 bytes;
+//  * backward lane: 4 channels, i.e. exactly one red.global.add.v4.f32 per corner.
+// D*elem must be a multiple of 16.
+#ifndef DCNB200_FWD_LANE_BYTES
+#define DCNB200_FWD_LANE_BYTES 32
+#endif
+#ifndef DCNB200_BWD_LANE_CH
+#define DCNB200_BWD_LANE_CH 4
+#endif
+template <typename P>
+int lane_geometry(P& p, int D, int dtype, bool wide_fwd, bool wide_bwd) {
   const int es = elem_size(dtype);
   if (D <= 0 || (D * es) % 16 != 0) return DCNV4B200_ERR_CHANNELS;
-  *vb = (wide_ok && (D * es) % 32 == 0) ? 32 : 16;
-  split_lanes(D, *vb / es, tpg, chunks);
-  split_lanes(D, 4, tpg_b, chunks_b);
+  int lane = 16 / es;
+  for (int cand = DCNB200_FWD_LANE_BYTES / es; cand * es > 16; cand /= 2)
+    if (D % cand == 0 && wide_fwd) { lane = cand; break; }
+  p.lane_ch = lane;
+  split_lanes(D, lane, &p.tpg, &p.chunks);
+  p.lane_ch_b = (DCNB200_BWD_LANE_CH == 8 && D % 8 == 0 && (es == 2 || wide_bwd)) ? 8 : 4;
+  split_lanes(D, p.lane_ch_b, &p.tpg_b, &p.chunks_b);
   return 0;
 }
 
 // 2-D query tile of one CTA for the DCNv4 kernels: at most `max_q` queries (what fits the
-// staging budget, capped so that a CTA keeps a few items per thread), as square as the
-// divisors of the output size allow, and small enough to leave a few CTAs per SM.
+// shared-memory budget, capped so that a CTA keeps a few items per thread), as square as the
+// divisors of the output size allow, and small enough to leave several tiles per SM.
 void pick_tile_2d(int N, int Ho, int Wo, size_t bytes_per_query, int items_per_query, int* th, int* tw) {
-  long long max_q = (long long)(kStageBytesMax / bytes_per_query);
+  long long max_q = (long long)(kSmemBudget / bytes_per_query);
   const long long cap_items = (6LL * kThreads + items_per_query - 1) / items_per_query;
   if (max_q > cap_items) max_q = cap_items;
-  const long long cap_grid = (long long)N * Ho * Wo / (148LL * 4);
+  const long long cap_grid = (long long)N * Ho * Wo / (148LL * 6);
   if (cap_grid >= 1 && max_q > cap_grid) max_q = cap_grid;
   if (max_q < 1) max_q = 1;
-  // width: the divisor of Wo closest to sqrt(max_q) from below (ragged tiles are allowed, but
-  // exact ones waste no lanes); fall back to min(Wo, 8)
+  // width: the largest divisor of Wo with w*w <= max_q (ragged tiles are allowed, but exact
+  // ones waste no lanes); fall back to min(Wo, 8, max_q)
   int best_w = 0;
   for (int w = 1; w <= Wo && (long long)w * w <= max_q; ++w)
     if (Wo % w == 0) best_w = w;
-  if (best_w < 4 && Wo >= 4) best_w = (int)(max_q < 8 ? max_q : 8) < Wo ? (int)(max_q < 8 ? max_q : 8) : Wo;
+  if (best_w < 4 && Wo >= 4) {
+    best_w = (int)(max_q < 8 ? max_q : 8);
+    if (best_w > Wo) best_w = Wo;
+  }
   if (best_w < 1) best_w = 1;
   long long h = max_q / best_w;
   if (h < 1) h = 1;
@@ -93,12 +126,12 @@ void pick_tile_2d(int N, int Ho, int Wo, size_t bytes_per_query, int items_per_q
 // never so many that the grid drops below a few CTAs per SM; `unit` keeps every tile start
 // 16-byte aligned.
 int pick_tile(long long nq, size_t bytes_per_query, int unit, int items_per_query) {
-  long long t = (long long)(kStageBytesMax / bytes_per_query);
+  long long t = (long long)(kSmemBudget / bytes_per_query);
   const long long cap_items = (6LL * kThreads + items_per_query - 1) / items_per_query;
   if (t > cap_items) t = cap_items;
-  const long long cap_grid = nq / (148LL * 4);
+  const long long cap_grid = nq / (148LL * 6);
   if (cap_grid >= 1 && t > cap_grid) t = cap_grid;
-  if (t > 64) t = 64;
+  if (t > 128) t = 128;
   t = (t / unit) * unit;
   if (t < unit) t = unit;
   return (int)t;
@@ -106,7 +139,7 @@ int pick_tile(long long nq, size_t bytes_per_query, int unit, int items_per_quer
 
 int fill_dcn(DcnParams& p, int dtype, int N, int H, int W, int G, int D, int kh, int kw, int sh, int sw,
              int ph, int pw, int dh, int dw, float offset_scale, int remove_center, int Ppad, int softmax,
-             bool backward, bool wide_ok = false) {
+             bool backward, bool wide_fwd = false, bool wide_bwd = false) {
   if (!dtype_ok(dtype)) return DCNV4B200_ERR_DTYPE;
   if (N <= 0 || H <= 0 || W <= 0 || G <= 0 || D <= 0 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 ||
       ph < 0 || pw < 0 || dh <= 0 || dw <= 0)
@@ -116,13 +149,14 @@ int fill_dcn(DcnParams& p, int dtype, int N, int H, int W, int G, int D, int kh,
   const int K = kh * kw - (remove_center ? 1 : 0);
   if (K <= 0) return DCNV4B200_ERR_SHAPE;
   if (Ppad % 8 != 0 || (long long)Ppad < 3LL * K * G) return DCNV4B200_ERR_PADDED_DIM;
-  if (int rc = lane_geometry(D, dtype, wide_ok, &p.vb, &p.tpg, &p.chunks, &p.tpg_b, &p.chunks_b)) return rc;
+  if (int rc = lane_geometry(p, D, dtype, wide_fwd, wide_bwd)) return rc;
   const long long nq = (long long)N * Ho * Wo;
   if (nq >= (1LL << 31) || (long long)H * W * G * D >= (1LL << 31) || (long long)G * D >= (1 << 24))
     return DCNV4B200_ERR_TOO_LARGE;
-  const size_t bpq = (size_t)Ppad * elem_size(dtype) + (backward ? (size_t)Ppad * 4 : 0) +
+  // shared memory per query: two staging buffers, the fp32 gradient rows (backward), softmax stats
+  const size_t bpq = 2 * (size_t)Ppad * elem_size(dtype) + (backward ? (size_t)Ppad * 4 : 0) +
                      (softmax ? (size_t)G * 8 : 0);
-  if (bpq > (size_t)kStageBytesMax) return DCNV4B200_ERR_UNSUPPORTED;
+  if (bpq + 64 > (size_t)kSmemBudget) return DCNV4B200_ERR_UNSUPPORTED;
   p.N = N; p.H = H; p.W = W; p.G = G; p.D = D; p.C = G * D; p.Ho = Ho; p.Wo = Wo;
   p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw; p.ph = ph; p.pw = pw; p.dh = dh; p.dw = dw;
   p.K = K; p.Ppad = Ppad; p.remove_center = remove_center ? 1 : 0; p.softmax = softmax ? 1 : 0;
@@ -132,15 +166,18 @@ int fill_dcn(DcnParams& p, int dtype, int N, int H, int W, int G, int D, int kh,
   p.tiles_x = (Wo + p.tw - 1) / p.tw;
   p.tiles_y = (Ho + p.th - 1) / p.th;
   if ((long long)N * p.tiles_x * p.tiles_y >= (1LL << 31)) return DCNV4B200_ERR_TOO_LARGE;
+  p.div_g = make_div(G);
+  p.div_tw = make_div(p.tw);
+  p.sm_count = 0;  // filled in by device_state() just before a launch
   return 0;
 }
 
 int fill_fda(FdaParams& p, int dtype, int B, int Len_in, int G, int D, int L, int Len_q, int K, bool backward,
-             bool wide_ok = false) {
+             bool wide_fwd = false, bool wide_bwd = false) {
   if (!dtype_ok(dtype)) return DCNV4B200_ERR_DTYPE;
   if (B <= 0 || Len_in <= 0 || G <= 0 || D <= 0 || L <= 0 || Len_q <= 0 || K <= 0) return DCNV4B200_ERR_SHAPE;
   if (L > kMaxLevels) return DCNV4B200_ERR_UNSUPPORTED;
-  if (int rc = lane_geometry(D, dtype, wide_ok, &p.vb, &p.tpg, &p.chunks, &p.tpg_b, &p.chunks_b)) return rc;
+  if (int rc = lane_geometry(p, D, dtype, wide_fwd, wide_bwd)) return rc;
   const long long nq = (long long)B * Len_q;
   if (nq >= (1LL << 31) || (long long)Len_in * G * D >= (1LL << 31) || (long long)G * D >= (1 << 24))
     return DCNV4B200_ERR_TOO_LARGE;
@@ -149,12 +186,14 @@ int fill_fda(FdaParams& p, int dtype, int B, int Len_in, int G, int D, int L, in
   // smallest number of queries whose rows span a multiple of 16 bytes
   int unit = 1;
   while ((row_bytes * unit) % 16 != 0) unit *= 2;
-  const size_t bpq = row_bytes + (backward ? (size_t)G * 3 * L * K * 4 : 0) + (size_t)G * 8;
-  if (bpq * unit + 64 > (size_t)kStageBytesMax) return DCNV4B200_ERR_UNSUPPORTED;
+  const size_t bpq = 2 * row_bytes + (backward ? (size_t)G * 3 * L * K * 4 : 0) + (size_t)G * 8;
+  if (bpq * unit + 128 > (size_t)kSmemBudget) return DCNV4B200_ERR_UNSUPPORTED;
   p.B = B; p.Len_in = Len_in; p.G = G; p.D = D; p.C = G * D; p.L = L; p.Len_q = Len_q; p.K = K; p.LK = L * K;
   p.nq = (int)nq;
   p.tile = pick_tile(nq, bpq, unit, G * (backward ? p.tpg_b : p.tpg));
-  while ((size_t)p.tile * bpq + 64 > (size_t)kStageBytesMax && p.tile > unit) p.tile -= unit;
+  while ((size_t)p.tile * bpq + 128 > (size_t)kSmemBudget && p.tile > unit) p.tile -= unit;
+  p.div_g = make_div(G);
+  p.sm_count = 0;
   return 0;
 }
 
@@ -174,7 +213,7 @@ const char* dcnv4b200_strerror(int code) {
     case DCNV4B200_ERR_WORKSPACE: return "workspace missing or smaller than *_bwd_workspace_bytes()";
     case DCNV4B200_ERR_UNSUPPORTED:
       return "outside the supported parameter space (more than 8 levels, or one query's packed row "
-             "exceeds the 40 KiB staging budget)";
+             "exceeds the shared-memory staging budget)";
     case DCNV4B200_ERR_PADDED_DIM: return "padded_offset_dim must be a multiple of 8 and >= 3*K*group";
     case DCNV4B200_ERR_CHANNELS: return "group_channels must be a multiple of 4 (fp32) or 8 (fp16/bf16)";
     case DCNV4B200_ERR_TOO_LARGE: return "tensor too large for 31-bit indexing";
@@ -204,7 +243,7 @@ int dcnv4b200_fwd(const void* value, const void* offset_mask, void* out, int dty
                         padded_offset_dim, softmax, false, aligned32(value) && aligned32(out)))
     return rc;
   int* status = nullptr;
-  if (int rc = status_ptr(&status)) return rc;
+  if (int rc = status_ptr(&status, &p.sm_count)) return rc;
   return (int)launch_dcnv4_fwd(dtype, value, offset_mask, out, p, status, static_cast<cudaStream_t>(stream));
 }
 
@@ -223,12 +262,12 @@ int dcnv4b200_bwd(const void* value, const void* offset_mask, const void* grad_o
     return DCNV4B200_ERR_ALIGN;
   DcnParams p;
   if (int rc = fill_dcn(p, dtype, N, H, W, G, D, kh, kw, sh, sw, ph, pw, dh, dw, offset_scale, remove_center,
-                        padded_offset_dim, softmax, true))
+                        padded_offset_dim, softmax, true, false, aligned32(value) && aligned32(grad_out)))
     return rc;
   const size_t need = dcnv4b200_bwd_workspace_bytes(dtype, N, H, W, G, D);
   if (need && (!workspace || workspace_bytes < need)) return DCNV4B200_ERR_WORKSPACE;
   int* status = nullptr;
-  if (int rc = status_ptr(&status)) return rc;
+  if (int rc = status_ptr(&status, &p.sm_count)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t n = (size_t)N * H * W * G * D;
   float* acc = need ? static_cast<float*>(workspace) : static_cast<float*>(grad_value);
@@ -249,7 +288,7 @@ int fdab200_fwd(const void* value, const int64_t* spatial_shapes, const int64_t*
   if (int rc = fill_fda(p, dtype, B, Len_in, G, D, L, Len_q, K, false, aligned32(value) && aligned32(out)))
     return rc;
   int* status = nullptr;
-  if (int rc = status_ptr(&status)) return rc;
+  if (int rc = status_ptr(&status, &p.sm_count)) return rc;
   return (int)launch_fda_fwd(dtype, value, spatial_shapes, level_start_index, sampling_loc_attn, out, p, status,
                              static_cast<cudaStream_t>(stream));
 }
@@ -270,11 +309,12 @@ int fdab200_bwd(const void* value, const int64_t* spatial_shapes, const int64_t*
       !aligned16(grad_sampling_loc_attn) || !aligned16(workspace))
     return DCNV4B200_ERR_ALIGN;
   FdaParams p;
-  if (int rc = fill_fda(p, dtype, B, Len_in, G, D, L, Len_q, K, true)) return rc;
+  if (int rc = fill_fda(p, dtype, B, Len_in, G, D, L, Len_q, K, true, false, aligned32(value) && aligned32(grad_out)))
+    return rc;
   const size_t need = fdab200_bwd_workspace_bytes(dtype, B, Len_in, G, D);
   if (need && (!workspace || workspace_bytes < need)) return DCNV4B200_ERR_WORKSPACE;
   int* status = nullptr;
-  if (int rc = status_ptr(&status)) return rc;
+  if (int rc = status_ptr(&status, &p.sm_count)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t n = (size_t)B * Len_in * G * D;
   float* acc = need ? static_cast<float*>(workspace) : static_cast<float*>(grad_value);
@@ -378,13 +418,13 @@ int dcnv4b200_bwd_static_scratch(const void* value, const void* offset_mask, con
     return DCNV4B200_ERR_ALIGN;
   DcnParams p;
   if (int rc = fill_dcn(p, dtype, N, H, W, G, D, kh, kw, sh, sw, ph, pw, dh, dw, offset_scale, remove_center,
-                        padded_offset_dim, softmax, true))
+                        padded_offset_dim, softmax, true, false, aligned32(value) && aligned32(grad_out)))
     return rc;
   const size_t n = (size_t)N * H * W * G * D;
   const bool needs_scratch = dtype != DCNV4B200_F32;
   if (needs_scratch && n > kStaticScratchFloats) return DCNV4B200_ERR_SCRATCH_LIMIT;
   int* status = nullptr;
-  if (int rc = status_ptr(&status)) return rc;
+  if (int rc = status_ptr(&status, &p.sm_count)) return rc;
   float* acc = static_cast<float*>(grad_value);
   if (needs_scratch) {
     if (int rc = static_scratch_ptr(&acc)) return rc;

@@ -2,16 +2,17 @@
 //
 // Conventions used by every kernel in this directory:
 //  * tensors are channels-last; a "pair" is one (query, group) and owns D contiguous channels;
-//  * forward: a lane owns a 32-byte channel vector of a pair (8 fp32 / 16 fp16-bf16 channels,
-//    one 256-bit load per bilinear corner; 16 bytes when D is too small), so a 16-channel
-//    fp16 group is one lane and the sampling arithmetic is not repeated per channel slice;
-//  * backward: a lane owns 4 channels, so its grad_value contribution to a corner is exactly
-//    one 16-byte vector reduction (red.global.add.v4.f32) and the lanes of a pair cover a
-//    contiguous 64-byte (D=16) span per instruction;
+//  * forward: a lane owns up to 16 channels of a pair (one 256-bit load per bilinear corner
+//    for fp16/bf16, two for fp32), so a 16-channel group is one lane and the sampling
+//    arithmetic of a point is never repeated per channel slice;
+//  * backward: a lane owns 8 channels (4 when D is not a multiple of 8): two 16-byte vector
+//    reductions (red.global.add.v4.f32) per corner into the fp32 accumulation buffer;
 //  * the lanes of a pair are adjacent, so offset/mask gradients are reduced with warp
 //    shuffles and never with per-element atomics;
-//  * a CTA owns a tile of queries whose packed offset/mask rows are staged into shared memory
-//    with bulk asynchronous copies (TMA 1-D, no multicast) completed on one mbarrier;
+//  * CTAs are persistent: each loops over query tiles, and while it works on one tile the
+//    packed offset/mask rows of its next tile are already in flight into the other half of a
+//    double-buffered shared-memory stage (bulk asynchronous copies, TMA 1-D, no multicast,
+//    one mbarrier per buffer, bounded waits);
 //  * all arithmetic is fp32 whatever the storage type; results are rounded once on store.
 #pragma once
 
@@ -22,8 +23,16 @@
 
 namespace dcnb200 {
 
+// Resident CTAs per SM the kernels are compiled for (bounds the registers per thread).
+#ifndef DCNB200_FWD_MINB
+#define DCNB200_FWD_MINB 2
+#endif
+#ifndef DCNB200_BWD_MINB
+#define DCNB200_BWD_MINB 2
+#endif
+
 constexpr int kThreads = 256;             // threads per CTA of the four main kernels
-constexpr int kStageBytesMax = 40 * 1024; // shared-memory budget for one staged tile
+constexpr int kSmemBudget = 72 * 1024;    // dynamic shared memory one CTA may use (3 CTAs per SM fit)
 constexpr int kMaxLevels = 8;             // FlashDeformAttn levels held in shared memory
 constexpr int kMaxTileRows = 32;          // rows of a 2-D query tile (one bulk copy per row)
 
@@ -41,34 +50,36 @@ template <> __device__ __forceinline__ float from_f32<float>(float v) { return v
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
-// Predicated read-only gathers of BYTES = 8, 16 or 32 bytes; `ok == false` yields zeros
-// (zero padding by omission).  The 32-byte form is a single 256-bit load
-// (ld.global.nc.v8.b32, new with sm_100).
+// 32 bytes of zeros.  A bilinear corner that lies outside the map is read from here instead
+// of being predicated off: the load stays unconditional (no per-register zero fill, no
+// predicate) and the out-of-map corner still contributes exactly zero.
+static __device__ __align__(32) const uint32_t g_zero_page[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+
+// Read-only gathers of BYTES = 8, 16 or 32 bytes; `ok == false` reads the zero page (zero
+// padding).  The 32-byte form is a single 256-bit load (ld.global.nc.v8.b32, new with sm_100).
 template <int BYTES> struct RawVec { uint32_t r[BYTES / 4]; };
 
 template <int BYTES>
 __device__ __forceinline__ RawVec<BYTES> ldg_raw(const void* p, bool ok);
 template <>
 __device__ __forceinline__ RawVec<8> ldg_raw<8>(const void* p, bool ok) {
-  RawVec<8> v; v.r[0] = 0u; v.r[1] = 0u;
-  if (ok) { const uint2 t = __ldg(reinterpret_cast<const uint2*>(p)); v.r[0] = t.x; v.r[1] = t.y; }
+  const uint2 t = __ldg(reinterpret_cast<const uint2*>(ok ? p : (const void*)g_zero_page));
+  RawVec<8> v; v.r[0] = t.x; v.r[1] = t.y;
   return v;
 }
 template <>
 __device__ __forceinline__ RawVec<16> ldg_raw<16>(const void* p, bool ok) {
-  RawVec<16> v; v.r[0] = v.r[1] = v.r[2] = v.r[3] = 0u;
-  if (ok) { const uint4 t = __ldg(reinterpret_cast<const uint4*>(p)); v.r[0] = t.x; v.r[1] = t.y; v.r[2] = t.z; v.r[3] = t.w; }
+  const uint4 t = __ldg(reinterpret_cast<const uint4*>(ok ? p : (const void*)g_zero_page));
+  RawVec<16> v; v.r[0] = t.x; v.r[1] = t.y; v.r[2] = t.z; v.r[3] = t.w;
   return v;
 }
 template <>
 __device__ __forceinline__ RawVec<32> ldg_raw<32>(const void* p, bool ok) {
   RawVec<32> v;
-  asm("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %9, 0;\n\t"
-      "mov.b32 %0, 0; mov.b32 %1, 0; mov.b32 %2, 0; mov.b32 %3, 0;\n\t"
-      "mov.b32 %4, 0; mov.b32 %5, 0; mov.b32 %6, 0; mov.b32 %7, 0;\n\t"
-      "@p ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n\t}"
+  const void* q = ok ? p : (const void*)g_zero_page;
+  asm("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
       : "=r"(v.r[0]), "=r"(v.r[1]), "=r"(v.r[2]), "=r"(v.r[3]), "=r"(v.r[4]), "=r"(v.r[5]), "=r"(v.r[6]), "=r"(v.r[7])
-      : "l"(p), "r"((int)ok));
+      : "l"(q));
   return v;
 }
 
@@ -171,78 +182,96 @@ __device__ __forceinline__ Footprint footprint(float h, float w, int H, int W) {
   return f;
 }
 
-// One sampling point of the forward pass: gather the four corners of V = VB/sizeof(T)
-// channels and accumulate m * bilinear.  `img` points at channel 0 of this lane in pixel (0,0).
-template <typename T, int VB>
-__device__ __forceinline__ void fwd_point(const T* __restrict__ img, int H, int W, int C, float h, float w,
-                                          float m, float (&acc)[VB / (int)sizeof(T)]) {
-  constexpr int V = VB / (int)sizeof(T);
-  const bool ok = in_range(h, w, (float)H, (float)W);
-  const Footprint f = footprint(h, w, H, W);
-  const T* p1 = img + (ptrdiff_t)((f.h0 * W + f.w0) * C);
-  const T* p3 = p1 + W * C;
-  const RawVec<VB> r1 = ldg_raw<VB>(p1, ok && f.top && f.left);
-  const RawVec<VB> r2 = ldg_raw<VB>(p1 + C, ok && f.top && f.right);
-  const RawVec<VB> r3 = ldg_raw<VB>(p3, ok && f.bot && f.left);
-  const RawVec<VB> r4 = ldg_raw<VB>(p3 + C, ok && f.bot && f.right);
-  const float a = m * f.hh, b = m * f.lh;
-  const float w1 = a * f.hw, w2 = a * f.lw, w3 = b * f.hw, w4 = b * f.lw;
-  float v[V];
-  widen(r1.r, v, (const T*)nullptr);
+// Gather V channels (V*sizeof(T) = 16, 32 or 64 bytes; 64 bytes = two 256-bit loads) of one
+// bilinear corner as fp32.
+template <typename T, int V>
+__device__ __forceinline__ void gather_corner(const T* p, bool ok, float (&v)[V]) {
+  constexpr int B = V * (int)sizeof(T);
+  if constexpr (B == 64) {
+    const RawVec<32> a = ldg_raw<32>(p, ok);
+    const RawVec<32> b = ldg_raw<32>(p + V / 2, ok);
+    float lo[V / 2], hi[V / 2];
+    widen(a.r, lo, (const T*)nullptr);
+    widen(b.r, hi, (const T*)nullptr);
 #pragma unroll
-  for (int e = 0; e < V; ++e) acc[e] = fmaf(w1, v[e], acc[e]);
-  widen(r2.r, v, (const T*)nullptr);
-#pragma unroll
-  for (int e = 0; e < V; ++e) acc[e] = fmaf(w2, v[e], acc[e]);
-  widen(r3.r, v, (const T*)nullptr);
-#pragma unroll
-  for (int e = 0; e < V; ++e) acc[e] = fmaf(w3, v[e], acc[e]);
-  widen(r4.r, v, (const T*)nullptr);
-#pragma unroll
-  for (int e = 0; e < V; ++e) acc[e] = fmaf(w4, v[e], acc[e]);
+    for (int e = 0; e < V / 2; ++e) { v[e] = lo[e]; v[V / 2 + e] = hi[e]; }
+  } else {
+    const RawVec<B> a = ldg_raw<B>(p, ok);
+    widen(a.r, v, (const T*)nullptr);
+  }
 }
 
-// One sampling point of the backward pass for a lane's 4 channels: scatter m*w_corner*gy into
-// the fp32 accumulation buffer and return this lane's share of
-//   gx = d(bilinear)/dw . gy,  gyv = d(bilinear)/dh . gy,  gm = bilinear . gy
-// (added to the running values so several channel chunks can be summed before the shuffle).
-// Returns whether the point passed the range test (false for inactive lanes).
-template <typename T>
-__device__ __forceinline__ bool bwd_point(const T* __restrict__ img, float* __restrict__ gimg, int H, int W,
-                                          int C, float h, float w, float m, bool active, const float (&gy)[4],
-                                          float& gx, float& gyv, float& gm) {
-  constexpr int LB = 4 * (int)sizeof(T);
-  const bool ok = active && in_range(h, w, (float)H, (float)W);
+// One sampling point of the forward pass: gather the four corners of this lane's V channels
+// and accumulate m * bilinear.  `img` points at channel 0 of this lane in pixel (0,0).
+template <typename T, int V>
+__device__ __forceinline__ void fwd_point(const T* __restrict__ img, int H, int W, int C, float Hf, float Wf,
+                                          float h, float w, float m, float (&acc)[V]) {
+  const bool ok = in_range(h, w, Hf, Wf);
   const Footprint f = footprint(h, w, H, W);
-  const ptrdiff_t pix = (ptrdiff_t)((f.h0 * W + f.w0) * C);
   const int row = W * C;
+  const int i1 = (f.h0 * W + f.w0) * C;
+  float v1[V], v2[V], v3[V], v4[V];
+  gather_corner<T, V>(img + i1, ok && f.top && f.left, v1);
+  gather_corner<T, V>(img + (i1 + C), ok && f.top && f.right, v2);
+  gather_corner<T, V>(img + (i1 + row), ok && f.bot && f.left, v3);
+  gather_corner<T, V>(img + (i1 + row + C), ok && f.bot && f.right, v4);
+  const float a = m * f.hh, b = m * f.lh;
+  const float w1 = a * f.hw, w2 = a * f.lw, w3 = b * f.hw, w4 = b * f.lw;
+#pragma unroll
+  for (int e = 0; e < V; ++e)
+    acc[e] = fmaf(w1, v1[e], fmaf(w2, v2[e], fmaf(w3, v3[e], fmaf(w4, v4[e], acc[e]))));
+}
+
+// One sampling point of the backward pass for a lane's V channels (V = 4 or 8): scatter
+// m*w_corner*gy into the fp32 accumulation buffer with 16-byte vector reductions and add this
+// lane's share of
+//   gx = d(bilinear)/dw . gy,  gyv = d(bilinear)/dh . gy,  gm = bilinear . gy
+// to the running values (so several channel chunks can be summed before the shuffle).
+// Returns whether the point passed the range test (false for inactive lanes).
+template <typename T, int V>
+__device__ __forceinline__ bool bwd_point(const T* __restrict__ img, float* __restrict__ gimg, int H, int W,
+                                          int C, float Hf, float Wf, float h, float w, float m, bool active,
+                                          const float (&gy)[V], float& gx, float& gyv, float& gm) {
+  const bool ok = active && in_range(h, w, Hf, Wf);
+  const Footprint f = footprint(h, w, H, W);
+  const int row = W * C;
+  const int i1 = (f.h0 * W + f.w0) * C;
   const bool ok1 = ok && f.top && f.left, ok2 = ok && f.top && f.right;
   const bool ok3 = ok && f.bot && f.left, ok4 = ok && f.bot && f.right;
-  const T* p1 = img + pix;
-  const RawVec<LB> r1 = ldg_raw<LB>(p1, ok1);
-  const RawVec<LB> r2 = ldg_raw<LB>(p1 + C, ok2);
-  const RawVec<LB> r3 = ldg_raw<LB>(p1 + row, ok3);
-  const RawVec<LB> r4 = ldg_raw<LB>(p1 + row + C, ok4);
+  float v1[V], v2[V], v3[V], v4[V];
+  gather_corner<T, V>(img + i1, ok1, v1);
+  gather_corner<T, V>(img + (i1 + C), ok2, v2);
+  gather_corner<T, V>(img + (i1 + row), ok3, v3);
+  gather_corner<T, V>(img + (i1 + row + C), ok4, v4);
   const float a = m * f.hh, b = m * f.lh;
   const float s1 = a * f.hw, s2 = a * f.lw, s3 = b * f.hw, s4 = b * f.lw;
-  float* a1 = gimg + pix;
-  if (ok1) red_add_v4(a1, s1 * gy[0], s1 * gy[1], s1 * gy[2], s1 * gy[3]);
-  if (ok2) red_add_v4(a1 + C, s2 * gy[0], s2 * gy[1], s2 * gy[2], s2 * gy[3]);
-  if (ok3) red_add_v4(a1 + row, s3 * gy[0], s3 * gy[1], s3 * gy[2], s3 * gy[3]);
-  if (ok4) red_add_v4(a1 + row + C, s4 * gy[0], s4 * gy[1], s4 * gy[2], s4 * gy[3]);
-  float v[4], d1, d2, d3, d4;
-  widen(r1.r, v, (const T*)nullptr);
-  d1 = fmaf(gy[0], v[0], fmaf(gy[1], v[1], fmaf(gy[2], v[2], gy[3] * v[3])));
-  widen(r2.r, v, (const T*)nullptr);
-  d2 = fmaf(gy[0], v[0], fmaf(gy[1], v[1], fmaf(gy[2], v[2], gy[3] * v[3])));
-  widen(r3.r, v, (const T*)nullptr);
-  d3 = fmaf(gy[0], v[0], fmaf(gy[1], v[1], fmaf(gy[2], v[2], gy[3] * v[3])));
-  widen(r4.r, v, (const T*)nullptr);
-  d4 = fmaf(gy[0], v[0], fmaf(gy[1], v[1], fmaf(gy[2], v[2], gy[3] * v[3])));
+#pragma unroll
+  for (int e = 0; e < V; e += 4) {
+    if (ok1) red_add_v4(gimg + (i1 + e), s1 * gy[e], s1 * gy[e + 1], s1 * gy[e + 2], s1 * gy[e + 3]);
+    if (ok2) red_add_v4(gimg + (i1 + C + e), s2 * gy[e], s2 * gy[e + 1], s2 * gy[e + 2], s2 * gy[e + 3]);
+    if (ok3) red_add_v4(gimg + (i1 + row + e), s3 * gy[e], s3 * gy[e + 1], s3 * gy[e + 2], s3 * gy[e + 3]);
+    if (ok4) red_add_v4(gimg + (i1 + row + C + e), s4 * gy[e], s4 * gy[e + 1], s4 * gy[e + 2], s4 * gy[e + 3]);
+  }
+  float d1 = 0.f, d2 = 0.f, d3 = 0.f, d4 = 0.f;  // sum_c gy_c * v_corner,c
+#pragma unroll
+  for (int e = 0; e < V; ++e) {
+    d1 = fmaf(gy[e], v1[e], d1);
+    d2 = fmaf(gy[e], v2[e], d2);
+    d3 = fmaf(gy[e], v3[e], d3);
+    d4 = fmaf(gy[e], v4[e], d4);
+  }
   gx += f.hh * (d2 - d1) + f.lh * (d4 - d3);
   gyv += f.hw * (d3 - d1) + f.lw * (d4 - d2);
   gm += f.hh * (f.hw * d1 + f.lw * d2) + f.lh * (f.hw * d3 + f.lw * d4);
   return ok;
+}
+
+// Division of a small non-negative int by a runtime constant without the integer-divide
+// sequence: q = umulhi(n, mul) with mul = floor(2^32/d) + 1 is exact while n*d < 2^32
+// (tile-local indices are a few thousand at most); d == 1 is passed through.
+struct FastDiv { uint32_t d, mul; };
+__device__ __forceinline__ int fast_div(int n, const FastDiv& f) {
+  return f.d == 1 ? n : (int)__umulhi((uint32_t)n, f.mul);
 }
 
 // ---------------------------------------------------------- mbarrier + bulk async copy (TMA)
@@ -274,33 +303,32 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
-// Stage `n_rows` spans of `row_bytes` each (global stride `src_stride` bytes, shared stride
-// `dst_stride` bytes; every address and stride 16-byte aligned) into shared memory.  Whole
-// 16-byte units go through bulk copies issued by thread 0 on one mbarrier; a ragged tail
-// (< 16 bytes, only possible when n_rows == 1) is copied with plain loads.  Returns false on
-// every thread of the CTA if the copies did not land within the bounded wait.
-__device__ __forceinline__ bool stage_rows(void* smem_dst, const void* gsrc, uint32_t row_bytes, int n_rows,
-                                           size_t src_stride, uint32_t dst_stride, uint64_t* bar, int* status) {
+// Issue (thread 0 only) the bulk copies of one staged tile: `n_rows` spans of `row_bytes`
+// each (global stride `src_stride` bytes, shared stride `dst_stride` bytes; every address and
+// stride 16-byte aligned), all completing on `bar`.  Only whole 16-byte units are copied; a
+// ragged tail (< 16 bytes, only possible when n_rows == 1) is left to copy_tail().
+__device__ __forceinline__ void issue_stage(void* smem_dst, const void* gsrc, uint32_t row_bytes, int n_rows,
+                                            size_t src_stride, uint32_t dst_stride, uint64_t* bar) {
   const uint32_t bulk = row_bytes & ~15u;
-  if (threadIdx.x == 0) mbar_init(bar, 1);
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    mbar_expect_tx(bar, bulk * (uint32_t)n_rows);
-    if (bulk)
-      for (int r = 0; r < n_rows; ++r)
-        bulk_g2s(static_cast<unsigned char*>(smem_dst) + (size_t)r * dst_stride,
-                 static_cast<const unsigned char*>(gsrc) + (size_t)r * src_stride, bulk, bar);
-  }
-  if (threadIdx.x >= 32 && threadIdx.x < 32 + (row_bytes - bulk) / 2u) {  // tail, 2-byte granules
-    const uint32_t i = bulk / 2u + (threadIdx.x - 32);
+  mbar_expect_tx(bar, bulk * (uint32_t)n_rows);
+  if (bulk)
+    for (int r = 0; r < n_rows; ++r)
+      bulk_g2s(static_cast<unsigned char*>(smem_dst) + (size_t)r * dst_stride,
+               static_cast<const unsigned char*>(gsrc) + (size_t)r * src_stride, bulk, bar);
+}
+// Ragged tail of a single-span stage, copied with plain 2-byte loads by a few threads.
+__device__ __forceinline__ void copy_tail(void* smem_dst, const void* gsrc, uint32_t row_bytes) {
+  const uint32_t bulk = row_bytes & ~15u;
+  if (threadIdx.x < (row_bytes - bulk) / 2u) {
+    const uint32_t i = bulk / 2u + threadIdx.x;
     reinterpret_cast<uint16_t*>(smem_dst)[i] = reinterpret_cast<const uint16_t*>(gsrc)[i];
   }
-  bool landed = mbar_wait_bounded(bar, 0);
-  if (!landed) {
-    atomicExch(status, kStatusStageTimeout);
-    mbar_wait_bounded(bar, 0);  // give the copies in flight one more bounded chance to finish
-  }
-  return __syncthreads_and(landed) != 0;
+}
+// Wait (bounded) for a staged tile.  A copy that never lands is recorded in the status word
+// and the CTA carries on: every gather and scatter is range-checked, so stale staging data
+// can produce wrong numbers but never an out-of-bounds access or a hang.
+__device__ __forceinline__ void wait_stage(uint64_t* bar, uint32_t parity, int* status) {
+  if (!mbar_wait_bounded(bar, parity)) atomicExch(status, kStatusStageTimeout);
 }
 
 // --------------------------------------------------------------------------- parameters
@@ -312,18 +340,21 @@ struct DcnParams {
   float scale;
   int th, tw;            // query tile (rows x columns) of one CTA
   int tiles_x, tiles_y;  // tiles per image
-  int vb;                // forward: bytes of a lane's channel vector (16 or 32)
-  int tpg, chunks;       // forward: D == (vb/elem) * tpg * chunks
-  int tpg_b, chunks_b;   // backward: D == 4 * tpg_b * chunks_b
+  int lane_ch, tpg, chunks;        // forward: D == lane_ch * tpg * chunks
+  int lane_ch_b, tpg_b, chunks_b;  // backward: D == lane_ch_b * tpg_b * chunks_b
   int nq;                // N*Ho*Wo
+  int sm_count;          // SMs of the current device (persistent grid sizing)
+  FastDiv div_g, div_tw;
 };
 
 struct FdaParams {
   int B, Len_in, G, D, C, L, Len_q, K, LK;
   int tile;              // consecutive queries per CTA
-  int vb, tpg, chunks;   // forward lane geometry
-  int tpg_b, chunks_b;   // backward lane geometry
+  int lane_ch, tpg, chunks;        // forward lane geometry
+  int lane_ch_b, tpg_b, chunks_b;  // backward lane geometry
   int nq;                // B*Len_q
+  int sm_count;
+  FastDiv div_g;
 };
 
 // Host-side launchers (one per kernel family).  dtype: 0 fp32, 1 fp16, 2 bf16.
@@ -340,6 +371,37 @@ cudaError_t launch_convert_f32(int dtype, const float* src, void* dst, size_t n,
 cudaError_t launch_dcnv4_corners(int dtype, const void* om, int32_t* corners, const DcnParams& p, cudaStream_t s);
 cudaError_t launch_fda_corners(int dtype, const int64_t* shapes, const void* sla, int32_t* corners,
                                const FdaParams& p, cudaStream_t s);
+
+// Resident CTAs per SM of a persistent kernel, without a runtime query per launch.  The first
+// launch of each kernel on each device raises its dynamic shared-memory limit to the budget
+// and reads its register count; afterwards the answer is arithmetic on the launch's
+// shared-memory size.  An over-estimate is harmless: CTAs never wait on one another, a CTA
+// that is not resident at once simply starts when a slot frees up.
+template <auto Kern>
+inline cudaError_t persistent_ctas_per_sm(size_t smem, int* per_sm) {
+  static int regs_limit[64] = {0};  // per device; written once with the same value by any thread
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  dev &= 63;
+  int lim = regs_limit[dev];
+  if (lim == 0) {
+    e = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e != cudaSuccess) return e;
+    cudaFuncAttributes a;
+    e = cudaFuncGetAttributes(&a, Kern);
+    if (e != cudaSuccess) return e;
+    const int regs_per_cta = ((a.numRegs + 7) / 8 * 8) * kThreads;
+    lim = regs_per_cta > 0 ? 65536 / regs_per_cta : 1;
+    if (lim < 1) lim = 1;
+    regs_limit[dev] = lim;
+  }
+  int by_smem = (int)((227u * 1024u) / (smem + 1024u));
+  int n = lim < by_smem ? lim : by_smem;
+  if (n > 2048 / kThreads) n = 2048 / kThreads;
+  *per_sm = n < 1 ? 1 : n;
+  return cudaSuccess;
+}
 
 size_t dcnv4_fwd_smem(const DcnParams& p, int elem);
 size_t dcnv4_bwd_smem(const DcnParams& p, int elem);

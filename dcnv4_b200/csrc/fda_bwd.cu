@@ -5,9 +5,10 @@
 // (DCNv4_op/src/cuda/flash_deform_col2im_cuda.cuh:20-580) and the zero-fills / fp16 casts
 // of DCNv4_op/src/cuda/flash_deform_attn_cuda.cu:125-131,157-162.
 //
-// Same structure as the DCNv4 backward (a lane owns 4 channels): vector reductions into an fp32 grad_value buffer,
-// shuffle reduction of the per-point partials over a pair's lanes, gradient rows assembled
-// in shared memory and written out whole.  The logit gradient uses
+// Same structure as the DCNv4 backward (a lane owns 8 channels): vector reductions into an
+// fp32 grad_value buffer, shuffle reduction of the per-point partials over a pair's lanes,
+// gradient rows assembled in shared memory and written out whole; persistent CTAs with a
+// double-buffered bulk-copy stage.  The logit gradient uses
 //   grad_logit_i = p_i * (g_i - sum_j g_j p_j),
 // which equals the reference's explicit Jacobian loop; a point that fails the range test
 // contributes g = 0 (the reference reads a never-written shared-memory slot there).
@@ -16,144 +17,177 @@
 namespace dcnb200 {
 
 size_t fda_bwd_smem(const FdaParams& p, int elem) {
-  const size_t row = ((size_t)p.tile * p.G * 3 * p.LK * elem + 15) & ~(size_t)15;
-  return 16 + row + (size_t)p.tile * p.G * 3 * p.LK * sizeof(float) + 16 + (size_t)p.tile * p.G * sizeof(float2);
+  const size_t n = (size_t)p.tile * p.G * 3 * p.LK;
+  const size_t span = (n * elem + 15) & ~(size_t)15;
+  const size_t gsz = (n * sizeof(float) + 15) & ~(size_t)15;
+  return 16 + 2 * span + gsz + (size_t)p.tile * p.G * sizeof(float2);
 }
 
-template <typename T, bool ONE_CHUNK>
-__global__ void __launch_bounds__(kThreads, 2)
+template <typename T, int V>
+__global__ void __launch_bounds__(kThreads, DCNB200_BWD_MINB)
 fda_bwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
                const int64_t* __restrict__ starts, const T* __restrict__ sla,
                const T* __restrict__ gout, float* __restrict__ gvalue, T* __restrict__ gsla,
                const FdaParams p, int* status) {
-  constexpr int LB = 4 * (int)sizeof(T);   // bytes a lane loads per corner (4 channels)
   constexpr int VS = 16 / (int)sizeof(T);  // elements per 16-byte store of the write-out
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int s_lvl[kMaxLevels * 3];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw);
-  T* s_row = reinterpret_cast<T*>(smem_raw + 16);
   const int rowlen = p.G * 3 * p.LK;
-  const size_t row_bytes = ((size_t)p.tile * rowlen * sizeof(T) + 15) & ~(size_t)15;
-  float* s_g = reinterpret_cast<float*>(smem_raw + 16 + row_bytes);
-  const size_t g_bytes = ((size_t)p.tile * rowlen * sizeof(float) + 15) & ~(size_t)15;
-  float2* s_stat = reinterpret_cast<float2*>(smem_raw + 16 + row_bytes + g_bytes);
+  const size_t sbytes = ((size_t)p.tile * rowlen * sizeof(T) + 15) & ~(size_t)15;
+  const size_t gbytes = ((size_t)p.tile * rowlen * sizeof(float) + 15) & ~(size_t)15;
+  T* s_buf[2] = {reinterpret_cast<T*>(smem_raw + 16), reinterpret_cast<T*>(smem_raw + 16 + sbytes)};
+  float* s_g = reinterpret_cast<float*>(smem_raw + 16 + 2 * sbytes);
+  float2* s_stat = reinterpret_cast<float2*>(smem_raw + 16 + 2 * sbytes + gbytes);
+  const int n_tiles = (p.nq + p.tile - 1) / p.tile;
 
-  const int q0 = blockIdx.x * p.tile;
-  const int nq_tile = min(p.tile, p.nq - q0);
+  auto issue = [&](int tile, int buf) {
+    const int q0 = tile * p.tile;
+    const int nq_tile = min(p.tile, p.nq - q0);
+    issue_stage(s_buf[buf], sla + (size_t)q0 * rowlen, (uint32_t)(nq_tile * rowlen * sizeof(T)), 1, 0, 0, &bar[buf]);
+  };
+
   if (threadIdx.x < p.L) {
     s_lvl[threadIdx.x * 3] = (int)shapes[threadIdx.x * 2];
     s_lvl[threadIdx.x * 3 + 1] = (int)shapes[threadIdx.x * 2 + 1];
     s_lvl[threadIdx.x * 3 + 2] = (int)starts[threadIdx.x];
   }
-  if (!stage_rows(s_row, sla + (size_t)q0 * rowlen, (uint32_t)(nq_tile * rowlen * sizeof(T)), 1, 0, 0, bar, status))
-    return;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && (int)blockIdx.x < n_tiles) issue(blockIdx.x, 0);
 
   const int LK = p.LK;
-  for (int pr = threadIdx.x; pr < nq_tile * p.G; pr += kThreads) {
-    const T* lg = s_row + pr * 3 * LK + 2 * LK;
-    float mx = -INFINITY;
-    for (int t = 0; t < LK; ++t) mx = fmaxf(mx, to_f32(lg[t]));
-    float sum = 0.f;
-    for (int t = 0; t < LK; ++t) sum += __expf(to_f32(lg[t]) - mx);
-    s_stat[pr] = make_float2(mx, 1.f / sum);
-  }
-  __syncthreads();
-
   const int tpg = p.tpg_b;
-  const int n_items = nq_tile * p.G * tpg;
-  for (int base = 0; base < n_items; base += kThreads) {
-    const bool active = base + threadIdx.x < n_items;
-    const int item = active ? base + threadIdx.x : 0;
-    const int c = item % tpg;
-    const int pr = item / tpg;
-    const int g = pr % p.G;
-    const int ql = pr / p.G;
-    const int q = q0 + ql;
-    const int b = q / p.Len_q;
-    const T* row = s_row + pr * 3 * LK;
-    float* grow = s_g + pr * 3 * LK;
-    const float2 stat = s_stat[pr];
-    const T* go_ptr = gout + (size_t)q * p.C + g * p.D + c * 4;
-    float gy0[4];
-    if (ONE_CHUNK) widen(ldg_raw<LB>(go_ptr, active).r, gy0, (const T*)nullptr);
+  const int tpg_shift = 31 - __clz(tpg);
 
-    float dot = 0.f;  // sum_t g_t p_t, kept by lane 0 of the pair
-    for (int l = 0; l < p.L; ++l) {
-      const int Hl = s_lvl[l * 3], Wl = s_lvl[l * 3 + 1];
-      const float Hf = (float)Hl, Wf = (float)Wl;
-      const size_t img_off = ((size_t)b * p.Len_in + s_lvl[l * 3 + 2]) * p.C + g * p.D + c * 4;
+  int it = 0;
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+    const int cur = it & 1;
+    const int next = tile + gridDim.x;
+    if (threadIdx.x == 0 && next < n_tiles) issue(next, cur ^ 1);
+    const int q0 = tile * p.tile;
+    const int nq_tile = min(p.tile, p.nq - q0);
+    T* s_row = s_buf[cur];
+    copy_tail(s_row, sla + (size_t)q0 * rowlen, (uint32_t)(nq_tile * rowlen * sizeof(T)));
+    wait_stage(&bar[cur], (uint32_t)((it >> 1) & 1), status);
+    __syncthreads();
+
+    for (int pr = threadIdx.x; pr < nq_tile * p.G; pr += kThreads) {
+      const T* lg = s_row + pr * 3 * LK + 2 * LK;
+      float mx = -INFINITY;
+      for (int t = 0; t < LK; ++t) mx = fmaxf(mx, to_f32(lg[t]));
+      float sum = 0.f;
+      for (int t = 0; t < LK; ++t) sum += __expf(to_f32(lg[t]) - mx);
+      s_stat[pr] = make_float2(mx, 1.f / sum);
+    }
+    __syncthreads();
+
+    const int n_items = nq_tile * p.G * tpg;
+    for (int base = 0; base < n_items; base += kThreads) {
+      const bool active = base + threadIdx.x < n_items;
+      const int item = active ? base + threadIdx.x : 0;
+      const int c = item & (tpg - 1);
+      const int pr = item >> tpg_shift;
+      const int ql = fast_div(pr, p.div_g);
+      const int g = pr - ql * p.G;
+      const int q = q0 + ql;
+      const int b = q / p.Len_q;
+      const T* row = s_row + pr * 3 * LK;
+      float* grow = s_g + pr * 3 * LK;
+      const float2 stat = s_stat[pr];
+      const T* go_ptr = gout + (size_t)q * p.C + g * p.D + c * V;
+      float gy0[V];
+      gather_corner<T, V>(go_ptr, active, gy0);
+
+      float dot = 0.f;  // sum_t g_t p_t, kept by lane 0 of the pair
+      for (int l = 0; l < p.L; ++l) {
+        const int Hl = s_lvl[l * 3], Wl = s_lvl[l * 3 + 1];
+        const float Hf = (float)Hl, Wf = (float)Wl;
+        const size_t img_off = ((size_t)b * p.Len_in + s_lvl[l * 3 + 2]) * p.C + g * p.D + c * V;
 #pragma unroll 2
-      for (int k = 0; k < p.K; ++k) {
-        const int t = l * p.K + k;
-        const float w_im = fda_coord(to_f32(row[2 * t]), Wf);
-        const float h_im = fda_coord(to_f32(row[2 * t + 1]), Hf);
-        const float m = __expf(to_f32(row[2 * LK + t]) - stat.x) * stat.y;
-        float gx = 0.f, gyv = 0.f, gm = 0.f;
-        bool ok;
-        if (ONE_CHUNK) {
-          ok = bwd_point<T>(value + img_off, gvalue + img_off, Hl, Wl, p.C, h_im, w_im, m, active, gy0, gx, gyv, gm);
-        } else {
-          ok = false;
-          for (int ci = 0; ci < p.chunks_b; ++ci) {
-            const int off = ci * tpg * 4;
-            float gy[4];
-            widen(ldg_raw<LB>(go_ptr + off, active).r, gy, (const T*)nullptr);
-            ok = bwd_point<T>(value + img_off + off, gvalue + img_off + off, Hl, Wl, p.C, h_im, w_im, m, active,
-                              gy, gx, gyv, gm);
+        for (int k = 0; k < p.K; ++k) {
+          const int t = l * p.K + k;
+          const float w_im = fda_coord(to_f32(row[2 * t]), Wf);
+          const float h_im = fda_coord(to_f32(row[2 * t + 1]), Hf);
+          const float m = __expf(to_f32(row[2 * LK + t]) - stat.x) * stat.y;
+          float gx = 0.f, gyv = 0.f, gm = 0.f;
+          bool ok = bwd_point<T, V>(value + img_off, gvalue + img_off, Hl, Wl, p.C, Hf, Wf, h_im, w_im, m, active,
+                                    gy0, gx, gyv, gm);
+          for (int ci = 1; ci < p.chunks_b; ++ci) {
+            const int off = ci * tpg * V;
+            float gy[V];
+            gather_corner<T, V>(go_ptr + off, active, gy);
+            ok = bwd_point<T, V>(value + img_off + off, gvalue + img_off + off, Hl, Wl, p.C, Hf, Wf, h_im, w_im, m,
+                                 active, gy, gx, gyv, gm);
+          }
+          for (int o = tpg >> 1; o > 0; o >>= 1) {
+            gx += __shfl_xor_sync(0xffffffffu, gx, o);
+            gyv += __shfl_xor_sync(0xffffffffu, gyv, o);
+            gm += __shfl_xor_sync(0xffffffffu, gm, o);
+          }
+          if (active && c == 0) {
+            grow[2 * t] = ok ? Wf * m * gx : 0.f;
+            grow[2 * t + 1] = ok ? Hf * m * gyv : 0.f;
+            const float gt = ok ? gm : 0.f;
+            grow[2 * LK + t] = gt;
+            dot = fmaf(gt, m, dot);
           }
         }
-        for (int o = tpg >> 1; o > 0; o >>= 1) {
-          gx += __shfl_xor_sync(0xffffffffu, gx, o);
-          gyv += __shfl_xor_sync(0xffffffffu, gyv, o);
-          gm += __shfl_xor_sync(0xffffffffu, gm, o);
-        }
-        if (active && c == 0) {
-          grow[2 * t] = ok ? Wf * m * gx : 0.f;
-          grow[2 * t + 1] = ok ? Hf * m * gyv : 0.f;
-          const float gt = ok ? gm : 0.f;
-          grow[2 * LK + t] = gt;
-          dot = fmaf(gt, m, dot);
+      }
+      if (active && c == 0) {
+        for (int t = 0; t < LK; ++t) {
+          const float m = __expf(to_f32(row[2 * LK + t]) - stat.x) * stat.y;
+          grow[2 * LK + t] = m * (grow[2 * LK + t] - dot);
         }
       }
     }
-    if (active && c == 0) {
-      for (int t = 0; t < LK; ++t) {
-        const float m = __expf(to_f32(row[2 * LK + t]) - stat.x) * stat.y;
-        grow[2 * LK + t] = m * (grow[2 * LK + t] - dot);
-      }
-    }
-  }
 
-  __syncthreads();
-  // write the tile's gradient rows: 16-byte vectors, then a ragged tail element by element
-  const int n_elem = nq_tile * rowlen;
-  const int n_vec = n_elem / VS;
-  T* dst = gsla + (size_t)q0 * rowlen;
-  for (int i = threadIdx.x; i < n_vec; i += kThreads) {
-    float v[VS];
+    __syncthreads();
+    // write the tile's gradient rows: 16-byte vectors, then a ragged tail element by element
+    const int n_elem = nq_tile * rowlen;
+    const int n_vec = n_elem / VS;
+    T* dst = gsla + (size_t)q0 * rowlen;
+    for (int i = threadIdx.x; i < n_vec; i += kThreads) {
+      float v[VS];
 #pragma unroll
-    for (int e = 0; e < VS; e += 4) {
-      const float4 f4 = *reinterpret_cast<const float4*>(s_g + (size_t)i * VS + e);
-      v[e] = f4.x; v[e + 1] = f4.y; v[e + 2] = f4.z; v[e + 3] = f4.w;
+      for (int e = 0; e < VS; e += 4) {
+        const float4 f4 = *reinterpret_cast<const float4*>(s_g + (size_t)i * VS + e);
+        v[e] = f4.x; v[e + 1] = f4.y; v[e + 2] = f4.z; v[e + 3] = f4.w;
+      }
+      uint32_t packed[4];
+      narrow(v, packed, (const T*)nullptr);
+      stg_raw(dst + (size_t)i * VS, packed);
     }
-    uint32_t packed[4];
-    narrow(v, packed, (const T*)nullptr);
-    stg_raw(dst + (size_t)i * VS, packed);
+    for (int i = n_vec * VS + threadIdx.x; i < n_elem; i += kThreads) dst[i] = from_f32<T>(s_g[i]);
+    __syncthreads();  // s_g, statistics and this staging buffer are free for the next tile
   }
-  for (int i = n_vec * VS + threadIdx.x; i < n_elem; i += kThreads) dst[i] = from_f32<T>(s_g[i]);
+}
+
+template <typename T, int V>
+static cudaError_t launch_v(const T* value, const int64_t* shapes, const int64_t* starts, const T* sla,
+                            const T* gout, float* gvalue, T* gsla, const FdaParams& p, int* status,
+                            cudaStream_t s) {
+  const size_t smem = fda_bwd_smem(p, sizeof(T));
+  auto kern = fda_bwd_kernel<T, V>;
+  int per_sm = 1;
+  cudaError_t e = persistent_ctas_per_sm<fda_bwd_kernel<T, V>>(smem, &per_sm);
+  if (e != cudaSuccess) return e;
+  const long long n_tiles = ((long long)p.nq + p.tile - 1) / p.tile;
+  const long long want = (long long)p.sm_count * per_sm;
+  kern<<<(int)(n_tiles < want ? n_tiles : want), kThreads, smem, s>>>(value, shapes, starts, sla, gout, gvalue,
+                                                                     gsla, p, status);
+  return cudaGetLastError();
 }
 
 template <typename T>
 static cudaError_t launch_t(const T* value, const int64_t* shapes, const int64_t* starts, const T* sla,
                             const T* gout, float* gvalue, T* gsla, const FdaParams& p, int* status,
                             cudaStream_t s) {
-  const int grid = (p.nq + p.tile - 1) / p.tile;
-  const size_t smem = fda_bwd_smem(p, sizeof(T));
-  if (p.chunks_b == 1)
-    fda_bwd_kernel<T, true><<<grid, kThreads, smem, s>>>(value, shapes, starts, sla, gout, gvalue, gsla, p, status);
-  else
-    fda_bwd_kernel<T, false><<<grid, kThreads, smem, s>>>(value, shapes, starts, sla, gout, gvalue, gsla, p, status);
-  return cudaGetLastError();
+  return p.lane_ch_b == 8 ? launch_v<T, 8>(value, shapes, starts, sla, gout, gvalue, gsla, p, status, s)
+                          : launch_v<T, 4>(value, shapes, starts, sla, gout, gvalue, gsla, p, status, s);
 }
 
 cudaError_t launch_fda_bwd(int dtype, const void* value, const int64_t* shapes, const int64_t* starts,

@@ -5,99 +5,152 @@
 // (DCNv4_op/src/cuda/flash_deform_im2col_cuda.cuh:129-451) and the zero-filled output of
 // DCNv4_op/src/cuda/flash_deform_attn_cuda.cu:60.
 //
-// A lane owns 32 bytes of channels (one 256-bit load per corner).  The softmax statistics (max, 1/sum) are computed once per (query, head) while the tile is
-// in shared memory -- not once per channel lane -- and the level table (H_l, W_l, start_l)
-// is read from device memory once per CTA instead of once per thread and level.
+// Persistent CTAs loop over tiles of consecutive queries; a tile's packed location/logit rows
+// are one contiguous span staged with a bulk copy into a double-buffered shared-memory
+// stage.  A lane owns up to 16 channels of a head.  The softmax statistics (max, 1/sum) are
+// computed once per (query, head) while the tile is in shared memory -- not once per channel
+// lane -- and the level table (H_l, W_l, start_l) is read from device memory once per CTA
+// instead of once per thread and level.
 #include "common.cuh"
 
 namespace dcnb200 {
 
-size_t fda_fwd_smem(const FdaParams& p, int elem) {
-  const size_t row = ((size_t)p.tile * p.G * 3 * p.LK * elem + 15) & ~(size_t)15;
-  return 16 + row + (size_t)p.tile * p.G * sizeof(float2);
+static size_t span_bytes(const FdaParams& p, int elem) {
+  return ((size_t)p.tile * p.G * 3 * p.LK * elem + 15) & ~(size_t)15;
 }
 
-template <typename T, int VB>
-__global__ void __launch_bounds__(kThreads, 2)
+size_t fda_fwd_smem(const FdaParams& p, int elem) {
+  return 16 + 2 * span_bytes(p, elem) + (size_t)p.tile * p.G * sizeof(float2);
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kThreads, DCNB200_FWD_MINB)
 fda_fwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
                const int64_t* __restrict__ starts, const T* __restrict__ sla, T* __restrict__ out,
                const FdaParams p, int* status) {
-  constexpr int V = VB / (int)sizeof(T);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int s_lvl[kMaxLevels * 3];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw);
-  T* s_row = reinterpret_cast<T*>(smem_raw + 16);
   const int rowlen = p.G * 3 * p.LK;  // elements per query
-  const size_t row_bytes = ((size_t)p.tile * rowlen * sizeof(T) + 15) & ~(size_t)15;
-  float2* s_stat = reinterpret_cast<float2*>(smem_raw + 16 + row_bytes);
+  const size_t sbytes = ((size_t)p.tile * rowlen * sizeof(T) + 15) & ~(size_t)15;
+  T* s_buf[2] = {reinterpret_cast<T*>(smem_raw + 16), reinterpret_cast<T*>(smem_raw + 16 + sbytes)};
+  float2* s_stat = reinterpret_cast<float2*>(smem_raw + 16 + 2 * sbytes);
+  const int n_tiles = (p.nq + p.tile - 1) / p.tile;
 
-  const int q0 = blockIdx.x * p.tile;
-  const int nq_tile = min(p.tile, p.nq - q0);
+  auto issue = [&](int tile, int buf) {
+    const int q0 = tile * p.tile;
+    const int nq_tile = min(p.tile, p.nq - q0);
+    issue_stage(s_buf[buf], sla + (size_t)q0 * rowlen, (uint32_t)(nq_tile * rowlen * sizeof(T)), 1, 0, 0, &bar[buf]);
+  };
+
   if (threadIdx.x < p.L) {
     s_lvl[threadIdx.x * 3] = (int)shapes[threadIdx.x * 2];
     s_lvl[threadIdx.x * 3 + 1] = (int)shapes[threadIdx.x * 2 + 1];
     s_lvl[threadIdx.x * 3 + 2] = (int)starts[threadIdx.x];
   }
-  if (!stage_rows(s_row, sla + (size_t)q0 * rowlen, (uint32_t)(nq_tile * rowlen * sizeof(T)), 1, 0, 0, bar, status))
-    return;
-
-  const int LK = p.LK;
-  for (int pr = threadIdx.x; pr < nq_tile * p.G; pr += kThreads) {
-    const T* lg = s_row + pr * 3 * LK + 2 * LK;
-    float mx = -INFINITY;
-    for (int t = 0; t < LK; ++t) mx = fmaxf(mx, to_f32(lg[t]));
-    float sum = 0.f;
-    for (int t = 0; t < LK; ++t) sum += __expf(to_f32(lg[t]) - mx);
-    s_stat[pr] = make_float2(mx, 1.f / sum);
+  if (threadIdx.x == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
   }
   __syncthreads();
+  if (threadIdx.x == 0 && (int)blockIdx.x < n_tiles) issue(blockIdx.x, 0);
 
-  const int n_items = nq_tile * p.G * p.tpg;
-  for (int item = threadIdx.x; item < n_items; item += kThreads) {
-    const int c = item % p.tpg;
-    const int pr = item / p.tpg;
-    const int g = pr % p.G;
-    const int ql = pr / p.G;
-    const int q = q0 + ql;
-    const int b = q / p.Len_q;
-    const T* row = s_row + pr * 3 * LK;
-    const float2 stat = s_stat[pr];
+  const int LK = p.LK;
+  const int tpg_shift = 31 - __clz(p.tpg);
 
-    for (int ci = 0; ci < p.chunks; ++ci) {
-      const int ch0 = (c + ci * p.tpg) * V;
-      float acc[V];
+  int it = 0;
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+    const int cur = it & 1;
+    const int next = tile + gridDim.x;
+    if (threadIdx.x == 0 && next < n_tiles) issue(next, cur ^ 1);
+    const int q0 = tile * p.tile;
+    const int nq_tile = min(p.tile, p.nq - q0);
+    T* s_row = s_buf[cur];
+    copy_tail(s_row, sla + (size_t)q0 * rowlen, (uint32_t)(nq_tile * rowlen * sizeof(T)));
+    wait_stage(&bar[cur], (uint32_t)((it >> 1) & 1), status);
+    __syncthreads();  // the tail (if any) is visible to every thread
+
+    for (int pr = threadIdx.x; pr < nq_tile * p.G; pr += kThreads) {
+      const T* lg = s_row + pr * 3 * LK + 2 * LK;
+      float mx = -INFINITY;
+      for (int t = 0; t < LK; ++t) mx = fmaxf(mx, to_f32(lg[t]));
+      float sum = 0.f;
+      for (int t = 0; t < LK; ++t) sum += __expf(to_f32(lg[t]) - mx);
+      s_stat[pr] = make_float2(mx, 1.f / sum);
+    }
+    __syncthreads();
+
+    const int n_items = nq_tile * p.G * p.tpg;
+    for (int item = threadIdx.x; item < n_items; item += kThreads) {
+      const int c = item & (p.tpg - 1);
+      const int pr = item >> tpg_shift;
+      const int ql = fast_div(pr, p.div_g);
+      const int g = pr - ql * p.G;
+      const int q = q0 + ql;
+      const int b = q / p.Len_q;
+      const T* row = s_row + pr * 3 * LK;
+      const float2 stat = s_stat[pr];
+
+      for (int ci = 0; ci < p.chunks; ++ci) {
+        const int ch0 = (c + ci * p.tpg) * V;
+        float acc[V];
 #pragma unroll
-      for (int e = 0; e < V; ++e) acc[e] = 0.f;
-      for (int l = 0; l < p.L; ++l) {
-        const int Hl = s_lvl[l * 3], Wl = s_lvl[l * 3 + 1];
-        const float Hf = (float)Hl, Wf = (float)Wl;
-        const T* img = value + ((size_t)b * p.Len_in + s_lvl[l * 3 + 2]) * p.C + g * p.D + ch0;
+        for (int e = 0; e < V; ++e) acc[e] = 0.f;
+        for (int l = 0; l < p.L; ++l) {
+          const int Hl = s_lvl[l * 3], Wl = s_lvl[l * 3 + 1];
+          const float Hf = (float)Hl, Wf = (float)Wl;
+          const T* img = value + ((size_t)b * p.Len_in + s_lvl[l * 3 + 2]) * p.C + g * p.D + ch0;
 #pragma unroll 4
-        for (int k = 0; k < p.K; ++k) {
-          const int t = l * p.K + k;
-          const float w_im = fda_coord(to_f32(row[2 * t]), Wf);
-          const float h_im = fda_coord(to_f32(row[2 * t + 1]), Hf);
-          const float m = __expf(to_f32(row[2 * LK + t]) - stat.x) * stat.y;
-          fwd_point<T, VB>(img, Hl, Wl, p.C, h_im, w_im, m, acc);
+          for (int k = 0; k < p.K; ++k) {
+            const int t = l * p.K + k;
+            const float w_im = fda_coord(to_f32(row[2 * t]), Wf);
+            const float h_im = fda_coord(to_f32(row[2 * t + 1]), Hf);
+            const float m = __expf(to_f32(row[2 * LK + t]) - stat.x) * stat.y;
+            fwd_point<T, V>(img, Hl, Wl, p.C, Hf, Wf, h_im, w_im, m, acc);
+          }
+        }
+        constexpr int WORDS = V * (int)sizeof(T) / 4;
+        uint32_t packed[WORDS];
+        narrow(acc, packed, (const T*)nullptr);
+        T* dst = out + (size_t)q * p.C + g * p.D + ch0;
+        if constexpr (WORDS == 16) {
+          uint32_t lo[8], hi[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { lo[e] = packed[e]; hi[e] = packed[8 + e]; }
+          stg_raw(dst, lo);
+          stg_raw(dst + V / 2, hi);
+        } else {
+          stg_raw(dst, packed);
         }
       }
-      uint32_t packed[VB / 4];
-      narrow(acc, packed, (const T*)nullptr);
-      stg_raw(out + (size_t)q * p.C + g * p.D + ch0, packed);
     }
+    __syncthreads();  // buffer and statistics are free for the tile after next
   }
+}
+
+template <typename T, int V>
+static cudaError_t launch_v(const T* value, const int64_t* shapes, const int64_t* starts, const T* sla,
+                            T* out, const FdaParams& p, int* status, cudaStream_t s) {
+  const size_t smem = fda_fwd_smem(p, sizeof(T));
+  auto kern = fda_fwd_kernel<T, V>;
+  int per_sm = 1;
+  cudaError_t e = persistent_ctas_per_sm<fda_fwd_kernel<T, V>>(smem, &per_sm);
+  if (e != cudaSuccess) return e;
+  const long long n_tiles = ((long long)p.nq + p.tile - 1) / p.tile;
+  const long long want = (long long)p.sm_count * per_sm;
+  kern<<<(int)(n_tiles < want ? n_tiles : want), kThreads, smem, s>>>(value, shapes, starts, sla, out, p, status);
+  return cudaGetLastError();
 }
 
 template <typename T>
 static cudaError_t launch_t(const T* value, const int64_t* shapes, const int64_t* starts, const T* sla,
                             T* out, const FdaParams& p, int* status, cudaStream_t s) {
-  const int grid = (p.nq + p.tile - 1) / p.tile;
-  const size_t smem = fda_fwd_smem(p, sizeof(T));
-  if (p.vb == 32)
-    fda_fwd_kernel<T, 32><<<grid, kThreads, smem, s>>>(value, shapes, starts, sla, out, p, status);
-  else
-    fda_fwd_kernel<T, 16><<<grid, kThreads, smem, s>>>(value, shapes, starts, sla, out, p, status);
-  return cudaGetLastError();
+  const int bytes = p.lane_ch * (int)sizeof(T);
+  if constexpr (sizeof(T) == 4) {
+    if (bytes == 64) return launch_v<T, 16>(value, shapes, starts, sla, out, p, status, s);
+  }
+  if (bytes == 32) return launch_v<T, 32 / (int)sizeof(T)>(value, shapes, starts, sla, out, p, status, s);
+  return launch_v<T, 16 / (int)sizeof(T)>(value, shapes, starts, sla, out, p, status, s);
 }
 
 cudaError_t launch_fda_fwd(int dtype, const void* value, const int64_t* shapes, const int64_t* starts,
