@@ -94,39 +94,61 @@ int lane_geometry(P& p, int D, int dtype, bool wide_fwd, bool wide_bwd) {
 // shared-memory budget, capped so that a CTA keeps a few items per thread), as square as the
 // divisors of the output size allow, and small enough to leave several tiles per SM.
 void pick_tile_2d(int N, int Ho, int Wo, size_t bytes_per_query, int items_per_query, int* th, int* tw) {
-  long long max_q = (long long)(kSmemBudget / bytes_per_query);
+  // The search below is pure arithmetic on its arguments; a small per-thread memo keeps it off
+  // the per-call path of a training loop that repeats the same few shapes.
+  struct Memo { int N, Ho, Wo, ipq; size_t bpq; int th, tw; };
+  constexpr int kMemo = 16;
+  thread_local Memo memo[kMemo] = {};
+  thread_local int memo_next = 0;
+  for (int i = 0; i < kMemo; ++i) {
+    const Memo& m = memo[i];
+    if (m.th && m.N == N && m.Ho == Ho && m.Wo == Wo && m.ipq == items_per_query && m.bpq == bytes_per_query) {
+      *th = m.th; *tw = m.tw;
+      return;
+    }
+  }
+  struct Save {
+    Memo* slot; int* th; int* tw;
+    ~Save() { slot->th = *th; slot->tw = *tw; }
+  } save{&memo[memo_next], th, tw};
+  memo[memo_next] = Memo{N, Ho, Wo, items_per_query, bytes_per_query, 0, 0};
+  memo_next = (memo_next + 1) % kMemo;
+  long long max_q = (long long)((kSmemBudget - 64) / bytes_per_query);  // 64: barriers + alignment slack
   const long long cap_items = (6LL * kThreads + items_per_query - 1) / items_per_query;
   if (max_q > cap_items) max_q = cap_items;
   const long long cap_grid = (long long)N * Ho * Wo / (148LL * 6);
   if (cap_grid >= 1 && max_q > cap_grid) max_q = cap_grid;
   if (max_q < 1) max_q = 1;
-  // width: the largest divisor of Wo with w*w <= max_q (ragged tiles are allowed, but exact
-  // ones waste no lanes); fall back to min(Wo, 8, max_q)
-  int best_w = 0;
-  for (int w = 1; w <= Wo && (long long)w * w <= max_q; ++w)
-    if (Wo % w == 0) best_w = w;
-  if (best_w < 4 && Wo >= 4) {
-    best_w = (int)(max_q < 8 ? max_q : 8);
-    if (best_w > Wo) best_w = Wo;
+  // Score every shape that fits: the fraction of lane slots doing useful work (items of a tile
+  // are processed in passes of kThreads), the fraction of the tile grid that lies inside the
+  // image (ragged edges), and a mild preference for compact, larger tiles (L1 locality).
+  double best = -1.0;
+  int bh = 1, bw = 1;
+  const int h_max = Ho < kMaxTileRows ? Ho : kMaxTileRows;
+  const int w_max = Wo < 64 ? Wo : 64;
+  for (int h = 1; h <= h_max; ++h) {
+    for (int w = 1; w <= w_max && (long long)h * w <= max_q; ++w) {
+      const long long items = (long long)h * w * items_per_query;
+      const long long passes = (items + kThreads - 1) / kThreads;
+      const double lane_eff = (double)items / (double)(passes * kThreads);
+      const long long covered = (long long)((Ho + h - 1) / h) * h * ((Wo + w - 1) / w) * w;
+      const double edge_eff = (double)Ho * Wo / (double)covered;
+      const int thin = h < w ? h : w;
+      const double compact = 1.0 - 0.5 / (double)thin;
+      const double size_bonus = 1.0 - 1.0 / (double)(4 + h * w);
+      const double score = lane_eff * edge_eff * compact * size_bonus;
+      if (score > best + 1e-9) { best = score; bh = h; bw = w; }
+    }
   }
-  if (best_w < 1) best_w = 1;
-  long long h = max_q / best_w;
-  if (h < 1) h = 1;
-  if (h > Ho) h = Ho;
-  if (h > kMaxTileRows) h = kMaxTileRows;
-  int best_h = 1;
-  for (int t = 1; t <= h; ++t)
-    if (Ho % t == 0) best_h = t;
-  if (best_h * 2 <= h) best_h = (int)h;  // no useful divisor: accept a ragged last tile row
-  *th = best_h;
-  *tw = best_w;
+  *th = bh;
+  *tw = bw;
 }
 
 // Queries per CTA of the 1-D tiles (FlashDeformAttn): as many as fit the staging budget, but
 // never so many that the grid drops below a few CTAs per SM; `unit` keeps every tile start
 // 16-byte aligned.
 int pick_tile(long long nq, size_t bytes_per_query, int unit, int items_per_query) {
-  long long t = (long long)(kSmemBudget / bytes_per_query);
+  long long t = (long long)((kSmemBudget - 128) / bytes_per_query);
   const long long cap_items = (6LL * kThreads + items_per_query - 1) / items_per_query;
   if (t > cap_items) t = cap_items;
   const long long cap_grid = nq / (148LL * 6);

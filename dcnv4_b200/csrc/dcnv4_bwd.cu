@@ -66,7 +66,12 @@ dcnv4_bwd_kernel(const T* __restrict__ value, const T* __restrict__ om, const T*
   for (int i = threadIdx.x; i < n_q * (p.Ppad - used); i += kThreads)
     s_g[(i / (p.Ppad - used)) * p.Ppad + used + i % (p.Ppad - used)] = 0.f;
   __syncthreads();
-  if (threadIdx.x == 0 && (int)blockIdx.x < n_tiles) issue(blockIdx.x, 0);
+  // this CTA's contiguous share of the tiles (consecutive tiles are spatial neighbours, so
+  // the halo pixels they share are still in this SM's L1); shares differ by at most one tile
+  const int share = n_tiles / (int)gridDim.x, extra = n_tiles % (int)gridDim.x;
+  const int tile_begin = (int)blockIdx.x * share + min((int)blockIdx.x, extra);
+  const int tile_end = tile_begin + share + ((int)blockIdx.x < extra ? 1 : 0);
+  if (threadIdx.x == 0 && tile_begin < tile_end) issue(tile_begin, 0);
 
   const int cw = (p.dw * (kw - 1)) >> 1, ch = (p.dh * (kh - 1)) >> 1;
   const int center = (kw / 2) * kh + (kh / 2);
@@ -77,10 +82,10 @@ dcnv4_bwd_kernel(const T* __restrict__ value, const T* __restrict__ om, const T*
   const float Hf = (float)p.H, Wf = (float)p.W;
 
   int it = 0;
-  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+  for (int tile = tile_begin; tile < tile_end; ++tile, ++it) {
     const int cur = it & 1;
-    const int next = tile + gridDim.x;
-    if (threadIdx.x == 0 && next < n_tiles) issue(next, cur ^ 1);
+    const int next = tile + 1;
+    if (threadIdx.x == 0 && next < tile_end) issue(next, cur ^ 1);
 
     const int b = tile / tiles_per_img;
     const int t_in = tile - b * tiles_per_img;
@@ -239,7 +244,10 @@ static cudaError_t launch_v(const T* value, const T* om, const T* gout, float* g
   auto kern = plain ? dcnv4_bwd_kernel<T, V, true> : dcnv4_bwd_kernel<T, V, false>;
   const long long n_tiles = (long long)p.N * p.tiles_x * p.tiles_y;
   const long long want = (long long)p.sm_count * per_sm;
-  const int grid = (int)(n_tiles < want ? n_tiles : want);
+  // Measured on B200: with thousands of tiles the reduction-bound backward runs ~10 % faster
+  // when every tile is its own short-lived CTA (their phases de-synchronise naturally); with
+  // few tiles per SM the persistent, double-buffered form wins.
+  const int grid = (int)((n_tiles < want || n_tiles >= 4 * want) ? n_tiles : want);
   kern<<<grid, kThreads, smem, s>>>(value, om, gout, gvalue, gom, p, status);
   return cudaGetLastError();
 }

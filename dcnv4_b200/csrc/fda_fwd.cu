@@ -53,16 +53,21 @@ fda_fwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
     mbar_init(&bar[1], 1);
   }
   __syncthreads();
-  if (threadIdx.x == 0 && (int)blockIdx.x < n_tiles) issue(blockIdx.x, 0);
+  // this CTA's contiguous share of the tiles (consecutive tiles are spatial neighbours, so
+  // the halo pixels they share are still in this SM's L1); shares differ by at most one tile
+  const int share = n_tiles / (int)gridDim.x, extra = n_tiles % (int)gridDim.x;
+  const int tile_begin = (int)blockIdx.x * share + min((int)blockIdx.x, extra);
+  const int tile_end = tile_begin + share + ((int)blockIdx.x < extra ? 1 : 0);
+  if (threadIdx.x == 0 && tile_begin < tile_end) issue(tile_begin, 0);
 
   const int LK = p.LK;
   const int tpg_shift = 31 - __clz(p.tpg);
 
   int it = 0;
-  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+  for (int tile = tile_begin; tile < tile_end; ++tile, ++it) {
     const int cur = it & 1;
-    const int next = tile + gridDim.x;
-    if (threadIdx.x == 0 && next < n_tiles) issue(next, cur ^ 1);
+    const int next = tile + 1;
+    if (threadIdx.x == 0 && next < tile_end) issue(next, cur ^ 1);
     const int q0 = tile * p.tile;
     const int nq_tile = min(p.tile, p.nq - q0);
     T* s_row = s_buf[cur];
