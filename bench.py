@@ -43,6 +43,8 @@ METRIC = "dcnv4_fwd_bwd_hbm_throughput"
 UNIT = "GB/s"
 WORKLOAD = "dcnv4_fwd+bwd sweep, FlashInternImage-T stage shapes, N=64/GPU, fp32+fp16"
 CPU_SAMPLE_N = 8
+MODEL_GLOBAL_BATCH = 256
+MODEL_ITERS = 10
 
 
 def algorithmic_bytes(N, HW, C, G, es):
@@ -218,6 +220,55 @@ class Case:
         assert rc == 0, rc
 
 
+def time_reference_cuda(torch, cases, reps=5):
+    """Per operator call: median device time of the reference CUDA extension (its own launch
+    specs), L2 flushed between runs, plus max |difference| to our result on the same inputs.
+    Returns None when the extension has not been built."""
+    try:
+        from oracle import ref_cuda
+        if not ref_cuda.available():
+            return None
+        ref_cuda.ext()
+    except Exception as exc:  # missing build, ABI mismatch, ...
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    flush = torch.empty(256 * 1024 * 1024 // 4, device=cases[0].value.device)
+    out = []
+    for c in cases:
+        a = (3, 3, 1, 1, 1, 1, 1, 1, c.G, D, 1.0, 0)
+        stream = torch.cuda.current_stream().cuda_stream
+        c.fwd(stream)
+        c.bwd(stream)
+        for which in ("fwd", "bwd"):
+            fn = ((lambda: ref_cuda.dcnv4_forward(c.value, c.om, *a)) if which == "fwd" else
+                  (lambda: ref_cuda.dcnv4_backward(c.value, c.om, c.gout, *a)))
+            try:
+                res = fn()
+                torch.cuda.synchronize()
+            except Exception as exc:
+                out.append({"op": f"dcnv4_{which}_{c.name}", "error": f"{type(exc).__name__}: {exc}"[:160]})
+                continue
+            ts = []
+            for _ in range(reps):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            if which == "fwd":
+                diff = (res.float() - c.out.float()).abs().max().item()
+            else:
+                diff = max((res[0].float() - c.gvalue.float()).abs().max().item(),
+                           (res[1].float() - c.gom.float()).abs().max().item())
+            nbytes = c.fwd_bytes if which == "fwd" else c.bwd_bytes
+            ms = statistics.median(ts)
+            out.append({"op": f"dcnv4_{which}_{c.name}", "ms": ms, "gbs": nbytes / ms / 1e6,
+                        "max_abs_diff_vs_ours": diff})
+            del res
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -315,13 +366,38 @@ def run_ours(args):
         e1.record()
         barrier()
         e2e_ms = e0.elapsed_time(e1)
+    # ---- the caller of the hot path: FlashInternImage-T inference, random-init weights, fp16,
+    #      batch sharded over the ranks (global batch 256), no collective
+    model_ms, model_batch = float("nan"), max(1, MODEL_GLOBAL_BATCH // world)
+    if not args.no_model and not args.case:
+        from dcnv4_b200.flash_intern_image import flash_intern_image
+        torch.manual_seed(0)
+        model = flash_intern_image("t").to(dev).half().eval()
+        images = torch.randn(model_batch, 3, 224, 224, device=dev, dtype=torch.float16)
+        with torch.no_grad():
+            for _ in range(3):
+                model(images)
+            barrier()
+            m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            m0.record()
+            for _ in range(MODEL_ITERS):
+                model(images)
+            m1.record()
+            barrier()
+        model_ms = m0.elapsed_time(m1) / MODEL_ITERS
+        del model, images
+    # ---- the reference's own CUDA kernels, recompiled unmodified for sm_100 (oracle/build_ref.py),
+    #      timed beside ours on the same tensors: "the kernel to beat".  Baseline leg only.
+    ref_cuda_ops = None
+    if rank == 0 and world == 1 and not args.case and not args.no_ref_cuda:
+        ref_cuda_ops = time_reference_cuda(torch, cases)
     if rank == 0:
         sampler.stop()
 
-    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
+    times = torch.tensor([elapsed_ms, e2e_ms, model_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = times.tolist()
+    elapsed_ms, e2e_ms, model_ms = times.tolist()
 
     if rank == 0:
         per_op = []
@@ -355,6 +431,11 @@ def run_ours(args):
                          "ms": dom["ms"], "algorithmic_bytes": dom["bytes"]},
             "ops": per_op,
             "clocks": sampler.summary(wall0, wall1),
+            "reference_cuda": ref_cuda_ops,
+            "flash_intern_image_t": None if model_ms != model_ms else {
+                "img_per_s": model_batch * world / model_ms * 1e3, "ms_per_batch": model_ms,
+                "batch_per_gpu": model_batch, "global_batch": model_batch * world, "dtype": "fp16",
+                "input": "224x224 synthetic", "weights": "random init", "parallelism": f"batch-sharded x{world}"},
         }
         if args.case or args.no_e2e:
             line["e2e"] = None
@@ -378,6 +459,8 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end arm (profiling runs)")
+    ap.add_argument("--no-model", action="store_true", help="skip the FlashInternImage-T throughput arm")
+    ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference CUDA extension")
     ap.add_argument("--case", default="", help="profiling aid: run only operator calls whose name contains "
                     "this text, e.g. fwd_56x56x64_fp32 (names are dcnv4_{fwd,bwd}_{HxWxC}_{fp32,fp16})")
     args = ap.parse_args()

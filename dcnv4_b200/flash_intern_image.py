@@ -1,0 +1,286 @@
+"""FlashInternImage backbone + classification head: the caller of the DCNv4 hot path.
+
+A restatement of classification/models/flash_intern_image.py (StemLayer :235-272,
+DownsampleLayer :276-304, MLPLayer :308-341, InternImageLayer :344-437, InternImageBlock
+:440-537, FlashInternImage :540-770) for the T/S/B/L classification models, without the timm
+dependency and without the InternImage-H/G extras (clip projector, level-2 post norms,
+residual post norms).  Module and parameter names follow the reference, so its released
+`.pth` state dicts load with `load_state_dict`.
+
+Layout: activations stay channels-last.  The stem and downsample convolutions see NHWC
+storage through `permute` views in `torch.channels_last` memory format (no transposition
+copies), and the tokens handed to `DCNv4` are the same storage viewed as (N, H*W, C).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+from torch import nn
+from torch.utils import checkpoint
+
+from .modules import DCNv4
+
+
+class _ToChannelsFirst(nn.Module):
+    def forward(self, x):
+        return x.permute(0, 3, 1, 2)
+
+
+class _ToChannelsLast(nn.Module):
+    def forward(self, x):
+        return x.permute(0, 2, 3, 1)
+
+
+def build_norm_layer(dim: int, norm_layer: str, in_format="channels_last", out_format="channels_last",
+                     eps: float = 1e-6) -> nn.Sequential:
+    """BN works channels-first, LN channels-last; format adapters are parameter-free members of
+    the Sequential so that parameter indices match the reference (flash_intern_image.py:34-56)."""
+    layers: List[nn.Module] = []
+    if norm_layer == "BN":
+        if in_format == "channels_last":
+            layers.append(_ToChannelsFirst())
+        layers.append(nn.BatchNorm2d(dim))
+        if out_format == "channels_last":
+            layers.append(_ToChannelsLast())
+    elif norm_layer == "LN":
+        if in_format == "channels_first":
+            layers.append(_ToChannelsLast())
+        layers.append(nn.LayerNorm(dim, eps=eps))
+        if out_format == "channels_first":
+            layers.append(_ToChannelsFirst())
+    else:
+        raise NotImplementedError(f"build_norm_layer does not support {norm_layer}")
+    return nn.Sequential(*layers)
+
+
+def build_act_layer(act_layer: str) -> nn.Module:
+    if act_layer == "ReLU":
+        return nn.ReLU(inplace=True)
+    if act_layer == "SiLU":
+        return nn.SiLU(inplace=True)
+    if act_layer == "GELU":
+        return nn.GELU()
+    raise NotImplementedError(f"build_act_layer does not support {act_layer}")
+
+
+class DropPath(nn.Module):
+    """Stochastic depth per sample (the reference takes it from timm)."""
+
+    def __init__(self, drop_prob: float = 0.0):
+        super().__init__()
+        self.drop_prob = float(drop_prob)
+
+    def forward(self, x):
+        if self.drop_prob == 0.0 or not self.training:
+            return x
+        keep = 1.0 - self.drop_prob
+        mask = x.new_empty((x.shape[0],) + (1,) * (x.dim() - 1)).bernoulli_(keep)
+        return x * mask / keep
+
+
+class StemLayer(nn.Module):
+    """Two stride-2 3x3 convolutions: (N,3,H,W) -> (N,H/4,W/4,C) channels-last."""
+
+    def __init__(self, in_chans=3, out_chans=96, act_layer="GELU", norm_layer="BN"):
+        super().__init__()
+        self.conv1 = nn.Conv2d(in_chans, out_chans // 2, kernel_size=3, stride=2, padding=1)
+        self.norm1 = build_norm_layer(out_chans // 2, norm_layer, "channels_first", "channels_first")
+        self.act = build_act_layer(act_layer)
+        self.conv2 = nn.Conv2d(out_chans // 2, out_chans, kernel_size=3, stride=2, padding=1)
+        self.norm2 = build_norm_layer(out_chans, norm_layer, "channels_first", "channels_last")
+
+    def forward(self, x):
+        x = x.contiguous(memory_format=torch.channels_last)
+        x = self.act(self.norm1(self.conv1(x)))
+        return self.norm2(self.conv2(x)).contiguous()
+
+
+class DownsampleLayer(nn.Module):
+    """Stride-2 3x3 convolution doubling the channels, on (N, H*W, C) tokens."""
+
+    def __init__(self, channels, norm_layer="LN"):
+        super().__init__()
+        self.conv = nn.Conv2d(channels, 2 * channels, kernel_size=3, stride=2, padding=1, bias=False)
+        self.norm = build_norm_layer(2 * channels, norm_layer, "channels_first", "channels_first")
+
+    def forward(self, x, shape: Tuple[int, int]):
+        H, W = shape
+        N, _, C = x.shape
+        x = self.conv(x.view(N, H, W, C).permute(0, 3, 1, 2))   # NHWC storage seen as channels_last NCHW
+        x = self.norm(x)
+        H, W = x.size(2), x.size(3)
+        return x.permute(0, 2, 3, 1).reshape(N, H * W, 2 * C), (H, W)
+
+
+class MLPLayer(nn.Module):
+    def __init__(self, in_features, hidden_features=None, out_features=None, act_layer="GELU",
+                 mlp_fc2_bias=False, drop=0.0):
+        super().__init__()
+        out_features = out_features or in_features
+        hidden_features = hidden_features or in_features
+        self.fc1 = nn.Linear(in_features, hidden_features, bias=True)
+        self.act = build_act_layer(act_layer)
+        self.fc2 = nn.Linear(hidden_features, out_features, bias=mlp_fc2_bias)
+        self.drop = nn.Dropout(drop)
+
+    def forward(self, x, shape=None):
+        return self.drop(self.fc2(self.drop(self.act(self.fc1(x)))))
+
+
+class InternImageLayer(nn.Module):
+    """x + dcn(norm1(x)); x + mlp(norm2(x)) -- or the post-norm / layer-scale variants."""
+
+    def __init__(self, core_op, channels, groups, mlp_ratio=4.0, drop=0.0, drop_path=0.0, act_layer="GELU",
+                 norm_layer="LN", post_norm=False, layer_scale=None, offset_scale=1.0, with_cp=False,
+                 dcn_output_bias=False, mlp_fc2_bias=False, dw_kernel_size=None):
+        super().__init__()
+        self.channels, self.groups, self.mlp_ratio, self.with_cp = channels, groups, mlp_ratio, with_cp
+        self.norm1 = build_norm_layer(channels, "LN")
+        self.post_norm = post_norm
+        self.dcn = core_op(channels=channels, group=groups, offset_scale=offset_scale,
+                           dw_kernel_size=dw_kernel_size, output_bias=dcn_output_bias)
+        self.drop_path = DropPath(drop_path) if drop_path > 0.0 else nn.Identity()
+        self.norm2 = build_norm_layer(channels, "LN")
+        self.mlp = MLPLayer(in_features=channels, hidden_features=int(channels * mlp_ratio),
+                            act_layer=act_layer, drop=drop, mlp_fc2_bias=mlp_fc2_bias)
+        self.layer_scale = layer_scale is not None
+        if self.layer_scale:
+            self.gamma1 = nn.Parameter(layer_scale * torch.ones(channels), requires_grad=True)
+            self.gamma2 = nn.Parameter(layer_scale * torch.ones(channels), requires_grad=True)
+
+    def _inner(self, x, shape):
+        g1 = self.gamma1 if self.layer_scale else 1.0
+        g2 = self.gamma2 if self.layer_scale else 1.0
+        if self.post_norm:
+            x = x + self.drop_path(g1 * self.norm1(self.dcn(x, shape)))
+            x = x + self.drop_path(g2 * self.norm2(self.mlp(x, shape)))
+        else:
+            x = x + self.drop_path(g1 * self.dcn(self.norm1(x), shape))
+            x = x + self.drop_path(g2 * self.mlp(self.norm2(x), shape))
+        return x
+
+    def forward(self, x, shape):
+        if self.with_cp and x.requires_grad:
+            return checkpoint.checkpoint(self._inner, x, shape, use_reentrant=False)
+        return self._inner(x, shape)
+
+
+class InternImageBlock(nn.Module):
+    """`depth` layers at one resolution, a final LayerNorm (pre-norm models) and the downsample."""
+
+    def __init__(self, core_op, channels, depth, groups, downsample=True, mlp_ratio=4.0, drop=0.0,
+                 drop_path=0.0, act_layer="GELU", norm_layer="LN", post_norm=False, offset_scale=0.5,
+                 layer_scale=None, with_cp=False, dcn_output_bias=False, mlp_fc2_bias=False,
+                 dw_kernel_size=None):
+        super().__init__()
+        self.channels, self.depth, self.post_norm = channels, depth, post_norm
+        self.blocks = nn.ModuleList([
+            InternImageLayer(core_op=core_op, channels=channels, groups=groups, mlp_ratio=mlp_ratio, drop=drop,
+                             drop_path=drop_path[i] if isinstance(drop_path, (list, tuple)) else drop_path,
+                             act_layer=act_layer, norm_layer=norm_layer, post_norm=post_norm,
+                             layer_scale=layer_scale, offset_scale=offset_scale, with_cp=with_cp,
+                             dcn_output_bias=dcn_output_bias, mlp_fc2_bias=mlp_fc2_bias,
+                             dw_kernel_size=dw_kernel_size)
+            for i in range(depth)])
+        if not self.post_norm:
+            self.norm = build_norm_layer(channels, "LN")
+        self.downsample = DownsampleLayer(channels=channels, norm_layer=norm_layer) if downsample else None
+
+    def forward(self, x, shape):
+        for blk in self.blocks:
+            x = blk(x, shape)
+        if not self.post_norm:
+            x = self.norm(x)
+        if self.downsample is not None:
+            x, shape = self.downsample(x, shape)
+        return x, shape
+
+
+class FlashInternImage(nn.Module):
+    """FlashInternImage-T/S/B/L classifier.  Defaults are the reference constructor's
+    (flash_intern_image.py:575-600); `CONFIGS` holds the released model settings."""
+
+    def __init__(self, core_op="DCNv4", channels=64, depths: Sequence[int] = (3, 4, 18, 5),
+                 groups: Sequence[int] = (3, 6, 12, 24), num_classes=1000, mlp_ratio=4.0, drop_rate=0.0,
+                 drop_path_rate=0.2, drop_path_type="linear", act_layer="GELU", norm_layer="LN",
+                 layer_scale=None, offset_scale=0.5, post_norm=False, cls_scale=1.5, with_cp=False,
+                 mlp_fc2_bias=False, dcn_output_bias=False, dw_kernel_size=None, **kwargs):
+        super().__init__()
+        if core_op != "DCNv4":
+            raise ValueError("this package provides the DCNv4 core operator only")
+        self.core_op, self.num_classes, self.depths = core_op, num_classes, list(depths)
+        self.num_levels = len(depths)
+        self.channels = channels
+        self.num_features = int(channels * 2 ** (self.num_levels - 1))
+        self.patch_embed = StemLayer(in_chans=3, out_chans=channels, act_layer=act_layer, norm_layer="BN")
+        self.pos_drop = nn.Dropout(p=drop_rate)
+        total = sum(depths)
+        dpr = [drop_path_rate * i / max(total - 1, 1) for i in range(total)]
+        if drop_path_type == "uniform":
+            dpr = [drop_path_rate] * total
+        self.levels = nn.ModuleList()
+        for i in range(self.num_levels):
+            self.levels.append(InternImageBlock(
+                core_op=DCNv4, channels=int(channels * 2 ** i), depth=depths[i], groups=groups[i],
+                mlp_ratio=mlp_ratio, drop=drop_rate, drop_path=dpr[sum(depths[:i]): sum(depths[:i + 1])],
+                act_layer=act_layer, norm_layer=norm_layer, post_norm=post_norm,
+                downsample=(i < self.num_levels - 1), layer_scale=layer_scale, offset_scale=offset_scale,
+                with_cp=with_cp, mlp_fc2_bias=mlp_fc2_bias, dcn_output_bias=dcn_output_bias,
+                dw_kernel_size=dw_kernel_size))
+        head_dim = int(self.num_features * cls_scale)
+        self.conv_head = nn.Sequential(
+            nn.Conv2d(self.num_features, head_dim, kernel_size=1, bias=False),
+            build_norm_layer(head_dim, "BN", "channels_first", "channels_first"),
+            build_act_layer(act_layer))
+        self.head = nn.Linear(head_dim, num_classes) if num_classes > 0 else nn.Identity()
+        self.avgpool = nn.AdaptiveAvgPool2d((1, 1))
+        self.apply(self._init_weights)
+        for m in self.modules():
+            if isinstance(m, DCNv4):
+                m._reset_parameters()
+
+    @staticmethod
+    def _init_weights(m):
+        if isinstance(m, nn.Linear):
+            nn.init.trunc_normal_(m.weight, std=0.02)
+            if m.bias is not None:
+                nn.init.constant_(m.bias, 0)
+        elif isinstance(m, nn.LayerNorm):
+            nn.init.constant_(m.bias, 0)
+            nn.init.constant_(m.weight, 1.0)
+
+    def forward_features(self, x):
+        x = self.patch_embed(x)                    # (N, H/4, W/4, C) channels-last
+        N, H, W, C = x.shape
+        x = self.pos_drop(x.view(N, H * W, C))
+        shape = (H, W)
+        for level in self.levels:
+            x, shape = level(x, shape)
+        h, w = shape
+        x = self.conv_head(x.view(N, h, w, -1).permute(0, 3, 1, 2))
+        return torch.flatten(self.avgpool(x), 1)
+
+    def forward(self, x):
+        return self.head(self.forward_features(x))
+
+
+# Released classification settings (classification/configs/flash_intern_image_{t,s,b}_1k_224.yaml,
+# flash_intern_image_l_22kto1k_384.yaml).
+CONFIGS = {
+    "t": dict(channels=64, depths=(4, 4, 18, 4), groups=(4, 8, 16, 32), offset_scale=1.0, mlp_ratio=4.0,
+              drop_path_rate=0.1),
+    "s": dict(channels=80, depths=(4, 4, 21, 4), groups=(5, 10, 20, 40), offset_scale=1.0, mlp_ratio=4.0,
+              drop_path_rate=0.4, layer_scale=1e-5, post_norm=True, dw_kernel_size=3),
+    "b": dict(channels=112, depths=(4, 4, 21, 4), groups=(7, 14, 28, 56), offset_scale=0.5, mlp_ratio=4.0,
+              drop_path_rate=0.5, layer_scale=1e-5, post_norm=True, dw_kernel_size=3),
+    "l": dict(channels=160, depths=(5, 5, 22, 5), groups=(10, 20, 40, 80), offset_scale=2.0, mlp_ratio=4.0,
+              drop_path_rate=0.1, layer_scale=1e-5, post_norm=True, dw_kernel_size=3,
+              dcn_output_bias=True, mlp_fc2_bias=True),
+}
+
+
+def flash_intern_image(size: str = "t", **overrides) -> FlashInternImage:
+    cfg = dict(CONFIGS[size])
+    cfg.update(overrides)
+    return FlashInternImage(**cfg)
