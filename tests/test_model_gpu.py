@@ -9,16 +9,10 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-class _OracleDCN(torch.autograd.Function):
-    """DCNv4Function stand-in that computes the forward with the CPU oracle."""
-
-    @staticmethod
-    def forward(ctx, x, om, kh, kw, sh, sw, ph, pw, dh, dw, G, D, scale, step, rc):
-        out = cref.dcnv4_forward(x.float().cpu(), om.float().cpu(), kh, kw, sh, sw, ph, pw, dh, dw, G, D, scale, rc)
-        return out.to(device=x.device, dtype=x.dtype)
-
-
-def test_tiny_model_matches_oracle_composition(monkeypatch):
+def test_every_dcn_layer_of_a_tiny_model_matches_the_oracle():
+    """Run a small FlashInternImage once, capture what each DCNv4 layer saw and produced, and
+    recompute every layer from its own weights with the CPU oracle as the core.  (Comparing only
+    the logits would mix in the amplification of 1e-6 differences by the random-init layers.)"""
     from dcnv4_b200 import flash_intern_image as fii
     from dcnv4_b200.modules import dcnv4 as dcn_mod
     torch.manual_seed(0)
@@ -29,13 +23,28 @@ def test_tiny_model_matches_oracle_composition(monkeypatch):
             if isinstance(m, dcn_mod.DCNv4):
                 m.offset_mask.weight.normal_(0, 0.2)
                 m.offset_mask.bias.uniform_(0, 1)
+    seen = []
+    hooks = [m.register_forward_hook(lambda mod, args, kwargs, out: seen.append((mod, args, kwargs, out)),
+                                     with_kwargs=True)
+             for m in model.modules() if isinstance(m, dcn_mod.DCNv4)]
     x = torch.randn(2, 3, 64, 96, device=DEV)
     with torch.no_grad():
         y = model(x)
-        monkeypatch.setattr(dcn_mod, "DCNv4Function", _OracleDCN)
-        y_ref = model(x)
-    assert y.shape == (2, 10)
-    torch.testing.assert_close(y, y_ref, rtol=1e-3, atol=1e-4)
+    for h in hooks:
+        h.remove()
+    assert y.shape == (2, 10) and torch.isfinite(y).all()
+    assert len(seen) == 5
+    for mod, args, kwargs, out in seen:
+        inp = args[0]
+        H, W = kwargs.get("shape") or args[1]
+        N, L, C = inp.shape
+        with torch.no_grad():
+            v = mod.value_proj(inp).reshape(N, H, W, C)
+            om = mod.offset_mask(inp).reshape(N, H, W, -1)
+            core = cref.dcnv4_forward(v.cpu(), om.cpu(), 3, 3, 1, 1, 1, 1, 1, 1, mod.group, mod.group_channels,
+                                      mod.offset_scale, 0)
+            ref = mod.output_proj(core.to(DEV).float().reshape(N, L, C))
+        torch.testing.assert_close(out, ref, rtol=1e-3, atol=1e-4)
 
 
 def test_flash_intern_image_t_fp16_inference_and_train_step():

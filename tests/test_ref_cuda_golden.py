@@ -41,10 +41,10 @@ def test_oracle_matches_reference_cuda_fda(name):
     out = cref.fda_forward(t["value"], t["spatial_shapes"], t["level_start_index"], t["sampling_loc_attn"], K)
     gv, gs = cref.fda_backward(t["value"], t["spatial_shapes"], t["level_start_index"], t["sampling_loc_attn"],
                                t["grad_out"], K)
-    torch.testing.assert_close(out[:, ::3], torch.from_numpy(Z[f"fda/{name}/out"]).double(), **FWD)
-    torch.testing.assert_close(gv[:, ::3], torch.from_numpy(Z[f"fda/{name}/grad_value"]).double(), **BWD)
+    torch.testing.assert_close(out[:, ::8], torch.from_numpy(Z[f"fda/{name}/out"]).double(), **FWD)
+    torch.testing.assert_close(gv[:, ::8], torch.from_numpy(Z[f"fda/{name}/grad_value"]).double(), **BWD)
     # location gradients carry a factor H_l / W_l (up to 30 here)
-    torch.testing.assert_close(gs[:, ::3], torch.from_numpy(Z[f"fda/{name}/grad_sla"]).double(), rtol=2e-3, atol=5e-3)
+    torch.testing.assert_close(gs[:, ::8], torch.from_numpy(Z[f"fda/{name}/grad_sla"]).double(), rtol=2e-3, atol=5e-3)
 
 
 @needs_file
@@ -71,9 +71,9 @@ def test_kernels_match_reference_cuda_fda(name):
                                         t["sampling_loc_attn"], 64, K)
     gv, gs = ops.flash_deform_attn_backward(t["value"], t["spatial_shapes"], t["level_start_index"],
                                             t["sampling_loc_attn"], t["grad_out"], 64, K)
-    torch.testing.assert_close(out[:, ::3].cpu(), torch.from_numpy(Z[f"fda/{name}/out"]), **FWD)
-    torch.testing.assert_close(gv[:, ::3].cpu(), torch.from_numpy(Z[f"fda/{name}/grad_value"]), **BWD)
-    torch.testing.assert_close(gs[:, ::3].cpu(), torch.from_numpy(Z[f"fda/{name}/grad_sla"]), rtol=2e-3, atol=5e-3)
+    torch.testing.assert_close(out[:, ::8].cpu(), torch.from_numpy(Z[f"fda/{name}/out"]), **FWD)
+    torch.testing.assert_close(gv[:, ::8].cpu(), torch.from_numpy(Z[f"fda/{name}/grad_value"]), **BWD)
+    torch.testing.assert_close(gs[:, ::8].cpu(), torch.from_numpy(Z[f"fda/{name}/grad_sla"]), rtol=2e-3, atol=5e-3)
 
 
 @needs_file
