@@ -43,6 +43,13 @@ METRIC = "dcnv4_fwd_bwd_hbm_throughput"
 UNIT = "GB/s"
 WORKLOAD = "dcnv4_fwd+bwd sweep, FlashInternImage-T stage shapes, N=64/GPU, fp32+fp16"
 CPU_SAMPLE_N = 8
+# dram__bytes_read.sum + dram__bytes_write.sum per operator call, from the ncu capture summarised in
+# profiles/dcnv4_stage1_N64_ncu.md (kernel only; for fp16 backward plus the zero-fill of the fp32
+# accumulation buffer, 51.4 MB, and the convert pass, 51.4 + 25.7 MB, which ncu was not asked to capture)
+NCU_TRAFFIC_BYTES = {
+    "dcnv4_fwd_56x56x64_fp32": 194.4e6, "dcnv4_fwd_56x56x64_fp16": 77.2e6,
+    "dcnv4_bwd_56x56x64_fp32": 351.1e6, "dcnv4_bwd_56x56x64_fp16": 199.4e6 + 128.5e6,
+}
 MODEL_GLOBAL_BATCH = 256
 MODEL_ITERS = 10
 
@@ -427,7 +434,7 @@ def run_ours(args):
                     "api": "dcnv4_b200.DCNv4Function.apply + backward, pinned host buffers"},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "kernel": dom["op"], "achieved": dom["gbs"], "peak": peak,
-                         "peak_kind": peak_kind, "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": None,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": NCU_TRAFFIC_BYTES.get(dom["op"]),
                          "ms": dom["ms"], "algorithmic_bytes": dom["bytes"]},
             "ops": per_op,
             "clocks": sampler.summary(wall0, wall1),
