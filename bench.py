@@ -276,6 +276,88 @@ def time_reference_cuda(torch, cases, reps=5):
     return out
 
 
+def time_flash_deform_attn(torch, lib, dev, with_reference, reps=5):
+    """FlashDeformAttn forward/backward at the Deformable-DETR encoder shape (8 x 20,197 positions,
+    levels 100x152, 50x76, 25x38, 13x19, 8 heads x 32 channels, 4 points per level), fp32 and fp16:
+    median device time per call through the C ABI, L2 flushed between runs, and the reference CUDA
+    extension on the same tensors when it is available."""
+    levels = ((100, 152), (50, 76), (25, 38), (13, 19))
+    B, G, Dh, K, L = 8, 8, 32, 4, 4
+    shapes = torch.tensor(levels, dtype=torch.int64, device=dev)
+    sizes = shapes[:, 0] * shapes[:, 1]
+    starts = torch.cat((sizes.new_zeros(1), sizes.cumsum(0)[:-1]))
+    Len = int(sizes.sum())
+    g = torch.Generator().manual_seed(7)
+    value32 = torch.randn(B, Len, G, Dh, generator=g)
+    sla32 = torch.cat((torch.rand(B, Len, G, 2 * L * K, generator=g), torch.randn(B, Len, G, L * K, generator=g)), -1)
+    gout32 = torch.randn(B, Len, G * Dh, generator=g)
+    flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)
+    ref = None
+    if with_reference:
+        try:
+            from oracle import ref_cuda
+            ref = ref_cuda if ref_cuda.available() and ref_cuda.ext() is not None else None
+        except Exception:
+            ref = None
+    stream = torch.cuda.current_stream().cuda_stream
+    out = []
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    for dtype, code, tag in ((torch.float32, 0, "fp32"), (torch.float16, 1, "fp16")):
+        v, sla, go = (x.to(device=dev, dtype=dtype) for x in (value32, sla32, gout32))
+        es = v.element_size()
+        y, gv, gs = torch.empty(B, Len, G * Dh, dtype=dtype, device=dev), torch.empty_like(v), torch.empty_like(sla)
+        ws_bytes = lib.fdab200_bwd_workspace_bytes(code, B, Len, G, Dh)
+        ws = torch.empty(max(ws_bytes, 16) // 4, dtype=torch.float32, device=dev)
+        fwd_bytes = es * (v.numel() + sla.numel() + y.numel())
+        bwd_bytes = fwd_bytes + es * (v.numel() + sla.numel())
+
+        def fwd():
+            rc = lib.fdab200_fwd(v.data_ptr(), shapes.data_ptr(), starts.data_ptr(), sla.data_ptr(), y.data_ptr(),
+                                 code, B, Len, G, Dh, L, Len, K, stream)
+            assert rc == 0, rc
+
+        def bwd():
+            rc = lib.fdab200_bwd(v.data_ptr(), shapes.data_ptr(), starts.data_ptr(), sla.data_ptr(), go.data_ptr(),
+                                 gv.data_ptr(), gs.data_ptr(), ws.data_ptr() if ws_bytes else None, ws_bytes,
+                                 code, B, Len, G, Dh, L, Len, K, stream)
+            assert rc == 0, rc
+
+        for which, fn, nbytes in (("fwd", fwd, fwd_bytes), ("bwd", bwd, bwd_bytes)):
+            ms = timed(fn)
+            row = {"op": f"fda_{which}_8x20197x8x32_{tag}", "ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
+            if ref is not None:
+                try:
+                    rfn = ((lambda: ref.fda_forward(v, shapes, starts, sla, K)) if which == "fwd" else
+                           (lambda: ref.fda_backward(v, shapes, starts, sla, go, K)))
+                    row["reference_cuda_ms"] = timed(rfn)
+                    res = rfn()
+                    if which == "fwd":
+                        row["max_abs_diff_vs_reference"] = (res.float() - y.float()).abs().max().item()
+                    else:
+                        row["max_abs_diff_vs_reference"] = max((res[0].float() - gv.float()).abs().max().item(),
+                                                               (res[1].float() - gs.float()).abs().max().item())
+                    del res
+                except Exception as exc:
+                    row["reference_cuda_error"] = f"{type(exc).__name__}: {exc}"[:160]
+            out.append(row)
+        del v, sla, go, y, gv, gs, ws
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -398,6 +480,9 @@ def run_ours(args):
     ref_cuda_ops = None
     if rank == 0 and world == 1 and not args.case and not args.no_ref_cuda:
         ref_cuda_ops = time_reference_cuda(torch, cases)
+    fda_ops = None
+    if rank == 0 and world == 1 and not args.case and not args.no_fda:
+        fda_ops = time_flash_deform_attn(torch, lib, dev, with_reference=not args.no_ref_cuda)
     if rank == 0:
         sampler.stop()
 
@@ -439,6 +524,7 @@ def run_ours(args):
             "ops": per_op,
             "clocks": sampler.summary(wall0, wall1),
             "reference_cuda": ref_cuda_ops,
+            "flash_deform_attn": fda_ops,
             "flash_intern_image_t": None if model_ms != model_ms else {
                 "img_per_s": model_batch * world / model_ms * 1e3, "ms_per_batch": model_ms,
                 "batch_per_gpu": model_batch, "global_batch": model_batch * world, "dtype": "fp16",
@@ -468,6 +554,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end arm (profiling runs)")
     ap.add_argument("--no-model", action="store_true", help="skip the FlashInternImage-T throughput arm")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference CUDA extension")
+    ap.add_argument("--no-fda", action="store_true", help="skip the FlashDeformAttn (Deformable-DETR shape) leg")
     ap.add_argument("--case", default="", help="profiling aid: run only operator calls whose name contains "
                     "this text, e.g. fwd_56x56x64_fp32 (names are dcnv4_{fwd,bwd}_{HxWxC}_{fp32,fp16})")
     args = ap.parse_args()

@@ -151,9 +151,10 @@ __device__ __forceinline__ float dcn_base(int p0, int c, float s) { return fmaf(
 __device__ __forceinline__ float dcn_coord(float base, float tap_dil, float off, float s) {
   return fmaf(tap_dil + off, s, base);
 }
-// FlashDeformAttn: round(loc*size) then subtract one half (two roundings, never fused).
+// FlashDeformAttn: loc*size - 0.5 as ONE fused multiply-add, which is what the reference
+// binary does (verified against its kernels on a B200 at samples whose product lands on x.5).
 __device__ __forceinline__ float fda_coord(float loc, float size) {
-  return __fsub_rn(__fmul_rn(loc, size), 0.5f);
+  return fmaf(loc, size, -0.5f);
 }
 __device__ __forceinline__ bool in_range(float h, float w, float H, float W) {
   return h > -1.f && w > -1.f && h < H && w < W;

@@ -22,9 +22,10 @@
  *
  * Parity pin: the DCNv4 half is pinned against the reference's own
  * pure-PyTorch core (classification/ops_dcnv3/functions/dcnv3_func.py:172-220)
- * through committed golden vectors.  The FlashDeformAttn half has no runnable
- * in-repo reference formula ("parity unpinned" by the reference's own tests);
- * it is pinned against an independent grid_sample + autograd formulation.
+ * through committed golden vectors.  The reference has no CPU formula for
+ * FlashDeformAttn; that half (and DCNv4 once more) is pinned against golden
+ * vectors produced by the reference's own CUDA kernels, compiled unmodified and
+ * run on a B200, and against an independent grid_sample + autograd formulation.
  *
  * Inputs are float32 arrays (fp16/bf16 test inputs are rounded to the storage
  * type first and then widened, so the oracle sees exactly the values the GPU
@@ -77,12 +78,14 @@ static inline float dcn_coord(float base, int tap_dil, float off, float s) {
   return fmaf((float)tap_dil + off, s, base);
 }
 
-/* FlashDeformAttn pixel coordinate: loc*size - 0.5 with the product rounded to
- * fp32 before the subtraction (flash_deform_im2col_cuda.cuh:188-189: the 0.5
- * literal is a double, so the compiler cannot fuse the two operations). */
+/* FlashDeformAttn pixel coordinate loc*size - 0.5 (flash_deform_im2col_cuda.cuh:188-189).  The
+ * reference binary evaluates it as ONE fused multiply-add: nvcc demotes the double literal's
+ * subtraction to fp32 and contracts it with the product.  Checked against the reference
+ * kernels run on a B200: at a sample whose product rounds to x.5 exactly, the two-rounding
+ * form selects the next row (floor 16, lh 0) while the reference and the fused form select
+ * floor 15 with lh just under 1 -- same value, different location gradient. */
 static inline float fda_coord(float loc, int size) {
-  volatile float prod = loc * (float)size;
-  return prod - 0.5f;
+  return fmaf(loc, (float)size, -0.5f);
 }
 
 static void softmax_f64(const float *logits, int n, double *p) {
