@@ -174,7 +174,7 @@ def run_reference(args):
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
     return 0
 
 
@@ -358,6 +358,12 @@ def time_flash_deform_attn(torch, lib, dev, with_reference, reps=5):
     return out
 
 
+def _note(msg):
+    """Progress note on stderr (stdout carries only the JSON line)."""
+    if os.environ.get("RANK", "0") == "0":
+        print(f"[bench] {msg}", file=sys.stderr, flush=True)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -402,6 +408,7 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    _note(f"world {world}: {len(ops)} operator calls per step, warming up")
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
@@ -422,6 +429,7 @@ def run_ours(args):
     barrier()
     wall1 = time.time()
     elapsed_ms = t_start.elapsed_time(t_end)
+    _note(f"timed region done: {elapsed_ms / args.steps:.3f} ms per step")
 
     # ---- end to end through the public autograd API with pinned host buffers
     host_in, host_out = [], []
@@ -486,6 +494,7 @@ def run_ours(args):
     if rank == 0:
         sampler.stop()
 
+    _note("all legs done, reducing times over ranks")
     times = torch.tensor([elapsed_ms, e2e_ms, model_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -538,7 +547,7 @@ def run_ours(args):
                                     "sample": desc, "ms_per_pass": ms}
         else:
             line["cpu_baseline"] = None
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
     return 0
