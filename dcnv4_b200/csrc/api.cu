@@ -370,6 +370,22 @@ int fdab200_fwd_corners(const int64_t* spatial_shapes, const void* sampling_loc_
                                  static_cast<cudaStream_t>(stream));
 }
 
+int dcnv4b200_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, int dtype,
+                            int param_dtype, long long rows, int C, float eps, void* stream) {
+  if (!x || !gamma || !beta || !y) return DCNV4B200_ERR_NULL;
+  if (!dtype_ok(dtype) || (param_dtype != DCNV4B200_F32 && param_dtype != dtype)) return DCNV4B200_ERR_DTYPE;
+  if (rows < 0 || C <= 0) return DCNV4B200_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(y)) return DCNV4B200_ERR_ALIGN;
+  if ((C * elem_size(dtype)) % 16 != 0) return DCNV4B200_ERR_CHANNELS;
+  if (C > layernorm_max_channels(dtype)) return DCNV4B200_ERR_UNSUPPORTED;
+  if (rows == 0) return 0;
+  int* status = nullptr;
+  int sms = 1;
+  if (int rc = status_ptr(&status, &sms)) return rc;
+  return (int)launch_layernorm_fwd(dtype, param_dtype, x, gamma, beta, y, rows, C, eps, sms,
+                                   static_cast<cudaStream_t>(stream));
+}
+
 int dcnv4b200_device_status(int* status_out) {
   if (!status_out) return DCNV4B200_ERR_NULL;
   int* status = nullptr;

@@ -404,6 +404,10 @@ inline cudaError_t persistent_ctas_per_sm(size_t smem, int* per_sm) {
   return cudaSuccess;
 }
 
+cudaError_t launch_layernorm_fwd(int dtype, int param_dtype, const void* x, const void* gamma, const void* beta,
+                                 void* y, long long rows, int C, float eps, int sm_count, cudaStream_t s);
+int layernorm_max_channels(int dtype);
+
 size_t dcnv4_fwd_smem(const DcnParams& p, int elem);
 size_t dcnv4_bwd_smem(const DcnParams& p, int elem);
 size_t fda_fwd_smem(const FdaParams& p, int elem);

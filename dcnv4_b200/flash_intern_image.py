@@ -19,6 +19,7 @@ import torch
 from torch import nn
 from torch.utils import checkpoint
 
+from . import ops
 from .modules import DCNv4
 
 
@@ -30,6 +31,21 @@ class _ToChannelsFirst(nn.Module):
 class _ToChannelsLast(nn.Module):
     def forward(self, x):
         return x.permute(0, 2, 3, 1)
+
+
+class LayerNorm(nn.LayerNorm):
+    """torch.nn.LayerNorm (same parameters, same state-dict keys) whose inference forward on CUDA
+    runs the library's channels-last kernel: the model normalises millions of rows of 64-512
+    channels, which the stock kernel handles one thread block per row.  Whenever autograd needs
+    the operation (training) or the kernel does not cover the input, the stock path runs."""
+
+    def forward(self, x):
+        needs_grad = torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad)
+        if (not needs_grad and self.elementwise_affine and self.bias is not None
+                and len(self.normalized_shape) == 1 and not torch.is_autocast_enabled()
+                and ops.layer_norm_supported(x, self.weight)):
+            return ops.layer_norm_forward(x, self.weight, self.bias, self.eps)
+        return super().forward(x)
 
 
 def build_norm_layer(dim: int, norm_layer: str, in_format="channels_last", out_format="channels_last",
@@ -46,7 +62,7 @@ def build_norm_layer(dim: int, norm_layer: str, in_format="channels_last", out_f
     elif norm_layer == "LN":
         if in_format == "channels_first":
             layers.append(_ToChannelsLast())
-        layers.append(nn.LayerNorm(dim, eps=eps))
+        layers.append(LayerNorm(dim, eps=eps))
         if out_format == "channels_first":
             layers.append(_ToChannelsFirst())
     else:
@@ -150,14 +166,16 @@ class InternImageLayer(nn.Module):
             self.gamma2 = nn.Parameter(layer_scale * torch.ones(channels), requires_grad=True)
 
     def _inner(self, x, shape):
-        g1 = self.gamma1 if self.layer_scale else 1.0
-        g2 = self.gamma2 if self.layer_scale else 1.0
         if self.post_norm:
-            x = x + self.drop_path(g1 * self.norm1(self.dcn(x, shape)))
-            x = x + self.drop_path(g2 * self.norm2(self.mlp(x, shape)))
+            a = self.norm1(self.dcn(x, shape))
+            x = x + self.drop_path(self.gamma1 * a if self.layer_scale else a)
+            m = self.norm2(self.mlp(x, shape))
+            x = x + self.drop_path(self.gamma2 * m if self.layer_scale else m)
         else:
-            x = x + self.drop_path(g1 * self.dcn(self.norm1(x), shape))
-            x = x + self.drop_path(g2 * self.mlp(self.norm2(x), shape))
+            a = self.dcn(self.norm1(x), shape)
+            x = x + self.drop_path(self.gamma1 * a if self.layer_scale else a)
+            m = self.mlp(self.norm2(x), shape)
+            x = x + self.drop_path(self.gamma2 * m if self.layer_scale else m)
         return x
 
     def forward(self, x, shape):
@@ -246,7 +264,7 @@ class FlashInternImage(nn.Module):
             nn.init.trunc_normal_(m.weight, std=0.02)
             if m.bias is not None:
                 nn.init.constant_(m.bias, 0)
-        elif isinstance(m, nn.LayerNorm):
+        elif isinstance(m, nn.LayerNorm):  # includes the LayerNorm subclass above
             nn.init.constant_(m.bias, 0)
             nn.init.constant_(m.weight, 1.0)
 
@@ -263,6 +281,36 @@ class FlashInternImage(nn.Module):
 
     def forward(self, x):
         return self.head(self.forward_features(x))
+
+
+class GraphedInference:
+    """Replay a model's inference forward as one CUDA graph for a fixed input shape.
+
+    A FlashInternImage-T forward is ~600 kernel launches of a few microseconds each; issued one by
+    one the host cannot keep a B200 busy.  The forward is captured once (on a side stream, after
+    warm-up) and replayed: `graphed(images)` copies the batch into the static input buffer,
+    replays, and returns the static output tensor (valid until the next call)."""
+
+    def __init__(self, model: nn.Module, example: torch.Tensor, warmup: int = 3):
+        if not example.is_cuda:
+            raise RuntimeError("GraphedInference needs a CUDA example input")
+        self.model = model.eval()
+        self.static_in = example.clone()
+        side = torch.cuda.Stream(device=example.device)
+        side.wait_stream(torch.cuda.current_stream(example.device))
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(max(1, warmup)):   # also triggers the library's once-per-device set-up
+                self.model(self.static_in)
+        torch.cuda.current_stream(example.device).wait_stream(side)
+        torch.cuda.synchronize(example.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.no_grad(), torch.cuda.graph(self.graph):
+            self.static_out = self.model(self.static_in)
+
+    def __call__(self, images: torch.Tensor) -> torch.Tensor:
+        self.static_in.copy_(images, non_blocking=True)
+        self.graph.replay()
+        return self.static_out
 
 
 # Released classification settings (classification/configs/flash_intern_image_{t,s,b}_1k_224.yaml,

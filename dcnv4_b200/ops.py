@@ -168,6 +168,36 @@ def flash_deform_attn_backward(value, spatial_shapes, level_start_index, samplin
     return [grad_value, grad_sla]
 
 
+def layer_norm_forward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float) -> torch.Tensor:
+    """LayerNorm over the last dimension of a contiguous CUDA tensor with the library's
+    channels-last kernel (forward only; no autograd).  Raises ValueError for sizes the kernel
+    does not cover -- callers that want a fallback check `layer_norm_supported` first."""
+    _check_tensor(x, "input")
+    _check_tensor(weight, "weight")
+    _check_tensor(bias, "bias")
+    C = x.shape[-1]
+    if weight.numel() != C or bias.numel() != C or weight.dtype != bias.dtype:
+        raise RuntimeError("weight and bias must have the size of the last dimension and one dtype")
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().dcnv4b200_layernorm_fwd(x.data_ptr(), weight.data_ptr(), bias.data_ptr(), y.data_ptr(),
+                                                _code(x), _code(weight), x.numel() // max(C, 1), C, float(eps),
+                                                _stream(x))
+    _lib.check(rc, "layer_norm_forward")
+    return y
+
+
+def layer_norm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """True when `layer_norm_forward` covers this input (dtype, size, layout)."""
+    if not (x.is_cuda and x.is_contiguous() and x.dtype in _DTYPES and x.numel() > 0):
+        return False
+    C, es = x.shape[-1], x.element_size()
+    if (C * es) % 16 != 0 or C > (1024 if es == 4 else 2048):
+        return False
+    return weight is not None and weight.is_cuda and weight.dtype in (torch.float32, x.dtype) \
+        and x.data_ptr() % 16 == 0
+
+
 def dcnv4_corners(p_offset, H, W, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, dilation_h,
                   dilation_w, group, offset_scale, remove_center) -> torch.Tensor:
     """(N,Ho,Wo,G,K,2) int32 corner indices the kernels select (test aid)."""

@@ -146,6 +146,19 @@ int fdab200_fwd_corners(const int64_t* spatial_shapes, const void* sampling_loc_
                         int dtype, int B, int G, int L, int Len_q, int K, void* stream);
 
 /*
+ * LayerNorm forward over the last (contiguous) dimension of a channels-last tensor:
+ * y[r,:] = (x[r,:] - mean_r) * rsqrt(var_r + eps) * gamma + beta, statistics in fp32.
+ * The FlashInternImage blocks around the operator normalise millions of short rows
+ * (C = 64..1280); the reference uses torch.nn.LayerNorm for them
+ * (classification/models/flash_intern_image.py:34-56) and has no kernel of its own.
+ *   x, y   (rows, C) in `dtype`; gamma, beta (C) in `param_dtype` (fp32 or the same as dtype)
+ * C*elem must be a multiple of 16 bytes and at most 1024 (fp32) / 2048 (fp16, bf16) channels;
+ * larger or odd sizes return DCNV4B200_ERR_UNSUPPORTED / _ERR_CHANNELS and launch nothing.
+ */
+int dcnv4b200_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, int dtype,
+                            int param_dtype, long long rows, int C, float eps, void* stream);
+
+/*
  * Read and clear the current device's kernel status word (0 = no kernel ever gave up on a
  * bounded wait for its staged tile).  Synchronises the device; meant for tests and
  * post-mortems, not for the hot path.  No counterpart in the reference.
