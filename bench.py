@@ -364,6 +364,45 @@ def _note(msg):
         print(f"[bench] {msg}", file=sys.stderr, flush=True)
 
 
+def time_model_with_reference_kernels(torch, model, images, iters=5):
+    """ms per forward of `model` with the reference CUDA extension as the DCNv4 core, stock LayerNorm
+    and no CUDA graph; None when the extension is not built."""
+    try:
+        from oracle import ref_cuda
+        if not ref_cuda.available():
+            return None
+        ref_cuda.ext()
+    except Exception:
+        return None
+    from dcnv4_b200 import flash_intern_image as fii
+    from dcnv4_b200.modules import dcnv4 as dcn_mod
+
+    class RefCore:
+        @staticmethod
+        def apply(x, om, kh, kw, sh, sw, ph, pw, dh, dw, G, Dg, scale, step, rc):
+            return ref_cuda.dcnv4_forward(x, om, kh, kw, sh, sw, ph, pw, dh, dw, G, Dg, scale, rc, step)
+
+    saved_fn, saved_flag = dcn_mod.DCNv4Function, fii.LayerNorm.use_library_kernel
+    dcn_mod.DCNv4Function, fii.LayerNorm.use_library_kernel = RefCore, False
+    try:
+        with torch.no_grad():
+            for _ in range(2):
+                model(images)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                model(images)
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+    except Exception as exc:
+        _note(f"reference-stack model leg failed: {type(exc).__name__}: {exc}")
+        return None
+    finally:
+        dcn_mod.DCNv4Function, fii.LayerNorm.use_library_kernel = saved_fn, saved_flag
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -468,6 +507,7 @@ def run_ours(args):
     # ---- the caller of the hot path: FlashInternImage-T inference, random-init weights, fp16,
     #      batch sharded over the ranks (global batch 256), no collective
     model_ms, model_batch = float("nan"), max(1, MODEL_GLOBAL_BATCH // world)
+    model_ref_ms = None
     if not args.no_model and not args.case:
         from dcnv4_b200.flash_intern_image import GraphedInference, flash_intern_image
         torch.manual_seed(0)
@@ -484,7 +524,12 @@ def run_ours(args):
         m1.record()
         barrier()
         model_ms = m0.elapsed_time(m1) / MODEL_ITERS
-        del graphed, model, images
+        del graphed
+        # the same network the way the reference stack executes it: eager launches, torch.nn.LayerNorm,
+        # and the reference's own CUDA operator (oracle/_ref) in place of ours.  Baseline leg, rank 0 only.
+        if rank == 0 and world == 1 and not args.no_ref_cuda:
+            model_ref_ms = time_model_with_reference_kernels(torch, model, images)
+        del model, images
     # ---- the reference's own CUDA kernels, recompiled unmodified for sm_100 (oracle/build_ref.py),
     #      timed beside ours on the same tensors: "the kernel to beat".  Baseline leg only.
     ref_cuda_ops = None
@@ -540,7 +585,10 @@ def run_ours(args):
                 "img_per_s": model_batch * world / model_ms * 1e3, "ms_per_batch": model_ms,
                 "batch_per_gpu": model_batch, "global_batch": model_batch * world, "dtype": "fp16",
                 "input": "224x224 synthetic", "weights": "random init", "parallelism": f"batch-sharded x{world}",
-                "execution": "CUDA graph replay per forward, input copied into the graph's buffer each iteration"},
+                "execution": "CUDA graph replay per forward, input copied into the graph's buffer each iteration",
+                "reference_stack_img_per_s": (model_batch / model_ref_ms * 1e3) if model_ref_ms else None,
+                "reference_stack": "same network, eager launches, torch.nn.LayerNorm, reference CUDA operator "
+                                   "(its forward is wrong at the 14x14 and 7x7 stages; timing only)"},
         }
         if args.case or args.no_e2e:
             line["e2e"] = None
