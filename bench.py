@@ -604,6 +604,77 @@ def run_ours(args):
     return 0
 
 
+def run_train_l(args):
+    """Optional workload (--workload train_l): FlashInternImage-L training step, random-init weights,
+    1024x1024 synthetic images, batch 2 per GPU, bf16 autocast, activation checkpointing as in the
+    released -L config, AdamW, DDP gradient all-reduce over NCCL when launched with torchrun.
+    Prints one JSON line with images/s (whole job, max step time over ranks)."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from dcnv4_b200.flash_intern_image import flash_intern_image
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(0)
+    size, res, batch = args.train_size, args.train_res, 2
+    model = flash_intern_image(size, with_cp=True).to(dev).train()
+    if world > 1:
+        model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], broadcast_buffers=False,
+                                                          gradient_as_bucket_view=True)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.05)
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    images = torch.randn(batch, 3, res, res, generator=g).to(dev)
+    labels = torch.randint(0, 1000, (batch,), generator=g).to(dev)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = F.cross_entropy(model(images).float(), labels)
+        loss.backward()
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        loss = step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item() / args.steps
+    if rank == 0:
+        print(json.dumps({
+            "metric": f"flash_intern_image_{size}_train_throughput", "value": batch * world / ms * 1e3, "unit": "img/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 autocast",
+            "data": "synthetic", "loss": float(loss.detach()),
+            "config": {"workload": f"FlashInternImage-{size.upper()} training step, {res}x{res}, batch {batch}/GPU, "
+                                   "AdamW, activation checkpointing, DDP all-reduce",
+                       "global_batch": batch * world, "parallelism": f"dp{world}"},
+            "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -617,9 +688,15 @@ def main():
     ap.add_argument("--no-fda", action="store_true", help="skip the FlashDeformAttn (Deformable-DETR shape) leg")
     ap.add_argument("--case", default="", help="profiling aid: run only operator calls whose name contains "
                     "this text, e.g. fwd_56x56x64_fp32 (names are dcnv4_{fwd,bwd}_{HxWxC}_{fp32,fp16})")
+    ap.add_argument("--workload", choices=("ops", "train_l"), default="ops",
+                    help="ops (default): the DCNv4 operator sweep; train_l: FlashInternImage-L training step")
+    ap.add_argument("--train-size", default="l", choices=("t", "s", "b", "l"))
+    ap.add_argument("--train-res", type=int, default=1024)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "train_l":
+        return run_train_l(args)
     return run_ours(args)
 
 
