@@ -2,11 +2,14 @@
 //
 // Conventions used by every kernel in this directory:
 //  * tensors are channels-last; a "pair" is one (query, group) and owns D contiguous channels;
-//  * forward: a lane owns up to 16 channels of a pair (one 256-bit load per bilinear corner
-//    for fp16/bf16, two for fp32), so a 16-channel group is one lane and the sampling
-//    arithmetic of a point is never repeated per channel slice;
-//  * backward: a lane owns 8 channels (4 when D is not a multiple of 8): two 16-byte vector
-//    reductions (red.global.add.v4.f32) per corner into the fp32 accumulation buffer;
+//  * forward: a lane owns 32 bytes of a pair's channels (a whole 16-channel fp16/bf16 group,
+//    half of an fp32 one; 16 bytes when size or alignment forbid) and fetches a bilinear
+//    corner with one 256-bit load, so the lanes of a pair cover the corner in ONE instruction;
+//  * backward: a lane owns 4 channels: exactly one 16-byte vector reduction
+//    (red.global.add.v4.f32) per corner into the fp32 accumulation buffer, the lanes of a pair
+//    again covering the corner's contiguous bytes in one instruction.  (The kernels are
+//    templates on the channels per lane; api.cu:lane_geometry picks these values from measured
+//    gather / reduction rates.);
 //  * the lanes of a pair are adjacent, so offset/mask gradients are reduced with warp
 //    shuffles and never with per-element atomics;
 //  * CTAs are persistent: each loops over query tiles, and while it works on one tile the

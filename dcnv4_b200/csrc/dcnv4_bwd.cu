@@ -5,15 +5,16 @@
 // plus the zero-fills and the fp16 cast passes of the host wrapper
 // (DCNv4_op/src/cuda/dcnv4_cuda.cu:133-139,169-174).
 //
-//  * A lane owns 8 channels of a pair (4 when D is not a multiple of 8).  Its grad_value
-//    contribution to a bilinear corner is two 16-byte vector reductions
-//    (red.global.add.v4.f32) into the fp32 accumulation buffer.
+//  * A lane owns 4 channels of a pair (V is a template parameter; 8 is also instantiated).  Its
+//    grad_value contribution to a bilinear corner is one 16-byte vector reduction
+//    (red.global.add.v4.f32) into the fp32 accumulation buffer, and the lanes of a pair cover
+//    the corner's contiguous bytes in one instruction.
 //  * The three per-point partials (d/dx, d/dy, d/dmask) are reduced over the lanes of a pair
 //    with warp shuffles.  Lane 0 of the pair deposits them in a shared-memory image of the
 //    tile's grad_offset_mask rows; the CTA then writes whole rows (pad columns included, as
 //    zeros) with coalesced 16-byte stores, so grad_offset_mask needs no memset.
-//  * Persistent CTAs, 2-D query tiles and double-buffered bulk-copy staging as in the forward
-//    kernel.
+//  * 2-D query tiles and double-buffered bulk-copy staging as in the forward kernel; persistent
+//    CTAs when there are few tiles, one CTA per tile when there are thousands (see launch_v).
 #include "common.cuh"
 
 namespace dcnb200 {

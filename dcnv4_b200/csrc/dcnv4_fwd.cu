@@ -10,16 +10,14 @@
 // L1).  A tile's packed offset/mask rows -- one contiguous span per tile row -- are staged to
 // shared memory with bulk copies, double-buffered so the next tile's rows arrive while the
 // current tile is computed.  Work items (query, group, channel vector) are laid out
-// channel-fastest so a warp's output store covers consecutive bytes.  A lane owns up to 16
-// channels: the sampling arithmetic of a point is done once per group.
+// channel-fastest so a warp's output store covers consecutive bytes.  A lane owns 32 bytes of
+// channels (V is a template parameter; 16- and 64-byte lanes exist for other group sizes).
 #include "common.cuh"
 
 namespace dcnb200 {
 
-static size_t tile_bytes(const DcnParams& p, int elem) { return (size_t)p.th * p.tw * p.Ppad * elem; }
-
 size_t dcnv4_fwd_smem(const DcnParams& p, int elem) {
-  size_t b = 16 + 2 * tile_bytes(p, elem);
+  size_t b = 16 + 2 * (size_t)p.th * p.tw * p.Ppad * elem;
   if (p.softmax) b += (size_t)p.th * p.tw * p.G * sizeof(float2);
   return b;
 }

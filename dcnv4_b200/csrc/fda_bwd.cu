@@ -5,7 +5,7 @@
 // (DCNv4_op/src/cuda/flash_deform_col2im_cuda.cuh:20-580) and the zero-fills / fp16 casts
 // of DCNv4_op/src/cuda/flash_deform_attn_cuda.cu:125-131,157-162.
 //
-// Same structure as the DCNv4 backward (a lane owns 8 channels): vector reductions into an
+// Same structure as the DCNv4 backward (a lane owns 4 channels): vector reductions into an
 // fp32 grad_value buffer, shuffle reduction of the per-point partials over a pair's lanes,
 // gradient rows assembled in shared memory and written out whole; persistent CTAs with a
 // double-buffered bulk-copy stage.  The logit gradient uses

@@ -7,7 +7,7 @@
 //
 // Persistent CTAs loop over tiles of consecutive queries; a tile's packed location/logit rows
 // are one contiguous span staged with a bulk copy into a double-buffered shared-memory
-// stage.  A lane owns up to 16 channels of a head.  The softmax statistics (max, 1/sum) are
+// stage.  A lane owns 32 bytes of a head's channels.  The softmax statistics (max, 1/sum) are
 // computed once per (query, head) while the tile is in shared memory -- not once per channel
 // lane -- and the level table (H_l, W_l, start_l) is read from device memory once per CTA
 // instead of once per thread and level.
