@@ -50,7 +50,7 @@ def build(ref_root: str = "/root/reference", force: bool = False) -> str:
         name, path = u
         obj = os.path.join(OUT, name + ".o")
         cmd = ["nvcc", "-x", "cu", *common, *nvcc_ref, *inc, "-c", path, "-o", obj]
-        r = subprocess.run(cmd, capture_output=True, text=True)
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=1800)
         if r.returncode != 0:
             sys.stderr.write(r.stdout[-4000:] + r.stderr[-4000:])
             raise RuntimeError(f"nvcc failed on {name}")
