@@ -285,6 +285,33 @@ class FlashInternImage(nn.Module):
         return self.head(self.forward_features(x))
 
 
+@torch.no_grad()
+def fold_batchnorm_(model: "FlashInternImage") -> "FlashInternImage":
+    """Inference-only rewrite, in place: fold the three BatchNorm2d layers of the network (stem
+    conv1/conv2, classification head conv) into the convolutions in front of them, using the
+    running statistics, and replace them by identities.  Saves three full passes over the largest
+    activations of the model.  The model must be in eval mode and is no longer trainable (nor
+    state-dict compatible) afterwards."""
+    if model.training:
+        raise RuntimeError("fold_batchnorm_ is for eval-mode models")
+
+    def fold(conv: nn.Conv2d, bn: nn.BatchNorm2d):
+        scale = bn.weight / torch.sqrt(bn.running_var + bn.eps)
+        conv.weight.mul_(scale.view(-1, 1, 1, 1).to(conv.weight.dtype))
+        bias = conv.bias if conv.bias is not None else torch.zeros_like(bn.running_mean)
+        new_bias = (bias.float() - bn.running_mean.float()) * scale.float() + bn.bias.float()
+        conv.bias = nn.Parameter(new_bias.to(conv.weight.dtype), requires_grad=False)
+
+    stem = model.patch_embed
+    fold(stem.conv1, stem.norm1[0])
+    stem.norm1[0] = nn.Identity()
+    fold(stem.conv2, stem.norm2[0])
+    stem.norm2[0] = nn.Identity()
+    fold(model.conv_head[0], model.conv_head[1][0])
+    model.conv_head[1][0] = nn.Identity()
+    return model
+
+
 class GraphedInference:
     """Replay a model's inference forward as one CUDA graph for a fixed input shape.
 

@@ -71,3 +71,37 @@ def test_flash_intern_image_t_fp16_inference_and_train_step():
     g = model.levels[0].blocks[0].dcn.offset_mask.weight.grad
     assert g is not None and torch.isfinite(g).all() and torch.isfinite(loss)
     opt.step()
+
+
+def test_batchnorm_folding_and_graphed_inference_reproduce_the_eager_model():
+    import copy
+    from dcnv4_b200.flash_intern_image import GraphedInference, flash_intern_image, fold_batchnorm_
+    torch.manual_seed(3)
+    model = flash_intern_image("t").to(DEV).eval()
+    with torch.no_grad():          # non-trivial BatchNorm statistics
+        for m in model.modules():
+            if isinstance(m, torch.nn.BatchNorm2d):
+                m.running_mean.normal_(0, 0.5)
+                m.running_var.uniform_(0.5, 2.0)
+                m.weight.uniform_(0.5, 1.5)
+                m.bias.normal_(0, 0.2)
+    x = torch.randn(3, 3, 224, 224, device=DEV)
+    tf32 = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False     # compare the folding itself, not TF32 rounding of scaled weights
+    try:
+        with torch.no_grad():
+            y = model(x)
+            folded = fold_batchnorm_(copy.deepcopy(model))
+            y_folded = folded(x)
+    finally:
+        torch.backends.cudnn.allow_tf32 = tf32
+    torch.testing.assert_close(y_folded, y, rtol=1e-3, atol=2e-4)
+    # graph replay vs eager: same kernels except for cuDNN/cuBLAS algorithm choices (TF32 convolutions)
+    graphed = GraphedInference(folded, x)
+    y_graph = graphed(x).clone()
+    torch.testing.assert_close(y_graph, y_folded, rtol=1e-2, atol=1e-3)
+    x2 = torch.randn_like(x)
+    with torch.no_grad():
+        y2 = graphed(x2).clone()
+        torch.testing.assert_close(y2, folded(x2), rtol=1e-2, atol=1e-3)
+    assert not torch.allclose(y2, y_graph)      # the replay really consumed the new input
