@@ -76,6 +76,12 @@ FastDiv make_div(int d) {
 #ifndef DCNB200_BWD_LANE_CH
 #define DCNB200_BWD_LANE_CH 4
 #endif
+#ifndef DCNB200_TILES_PER_SM
+#define DCNB200_TILES_PER_SM 6
+#endif
+#ifndef DCNB200_MIN_PASSES
+#define DCNB200_MIN_PASSES 1
+#endif
 template <typename P>
 int lane_geometry(P& p, int D, int dtype, bool wide_fwd, bool wide_bwd) {
   const int es = elem_size(dtype);
@@ -116,8 +122,12 @@ void pick_tile_2d(int N, int Ho, int Wo, size_t bytes_per_query, int items_per_q
   long long max_q = (long long)((kSmemBudget - 64) / bytes_per_query);  // 64: barriers + alignment slack
   const long long cap_items = (6LL * kThreads + items_per_query - 1) / items_per_query;
   if (max_q > cap_items) max_q = cap_items;
-  const long long cap_grid = (long long)N * Ho * Wo / (148LL * 6);
-  if (cap_grid >= 1 && max_q > cap_grid) max_q = cap_grid;
+  // Several tiles per SM -- but a tile never shrinks below DCNB200_MIN_PASSES full passes of
+  // the CTA's threads: on a small batch idle lanes cost more than idle SMs.
+  long long cap_grid = (long long)N * Ho * Wo / (148LL * DCNB200_TILES_PER_SM);
+  const long long min_q = ((long long)DCNB200_MIN_PASSES * kThreads + items_per_query - 1) / items_per_query;
+  if (cap_grid < min_q) cap_grid = min_q;
+  if (max_q > cap_grid) max_q = cap_grid;
   if (max_q < 1) max_q = 1;
   // Score every shape that fits: the fraction of lane slots doing useful work (items of a tile
   // are processed in passes of kThreads), the fraction of the tile grid that lies inside the
@@ -151,7 +161,7 @@ int pick_tile(long long nq, size_t bytes_per_query, int unit, int items_per_quer
   long long t = (long long)((kSmemBudget - 128) / bytes_per_query);
   const long long cap_items = (6LL * kThreads + items_per_query - 1) / items_per_query;
   if (t > cap_items) t = cap_items;
-  const long long cap_grid = nq / (148LL * 6);
+  const long long cap_grid = nq / (148LL * DCNB200_TILES_PER_SM);
   if (cap_grid >= 1 && t > cap_grid) t = cap_grid;
   if (t > 128) t = 128;
   t = (t / unit) * unit;
