@@ -411,6 +411,11 @@ cudaError_t launch_layernorm_fwd(int dtype, int param_dtype, const void* x, cons
                                  void* y, long long rows, int C, float eps, int sm_count, cudaStream_t s);
 int layernorm_max_channels(int dtype);
 
+// y = epilogue(x . W^T + bias) on the tensor cores (linear.cu); dtype 1 fp16 / 2 bf16.
+cudaError_t launch_linear_fwd(int dtype, const void* x, const void* w, const void* bias, const void* residual,
+                              void* y, long long M, int N, int K, int act, int sms, int* status,
+                              cudaStream_t stream);
+
 size_t dcnv4_fwd_smem(const DcnParams& p, int elem);
 size_t dcnv4_bwd_smem(const DcnParams& p, int elem);
 size_t fda_fwd_smem(const FdaParams& p, int elem);

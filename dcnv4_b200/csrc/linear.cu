@@ -1,0 +1,614 @@
+// Linear layer with a fused epilogue on the 5th-generation tensor cores (tcgen05, sm_100a):
+//
+//     y[m, :] = epilogue( x[m, :] . W^T + bias )           x (M,K), W (N,K), y (M,N), 16-bit
+//
+// FlashInternImage wraps every DCNv4 operator in 1x1 projections and an MLP whose GELU and
+// residual additions the reference runs as separate element-wise kernels
+// (classification/models/flash_intern_image.py:308-341 MLPLayer, :414-432 residual adds).  At
+// inference those kernels move more bytes than the matrix products they follow.  Here the
+// activation / residual is applied to the accumulator on its way out of tensor memory, so the
+// intermediate never goes to HBM.
+//
+// One persistent CTA per SM, eighteen warps with fixed roles:
+//   warp 0     producer : TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) loads of the x tile
+//                         (128 x 64) and W tile (BN x 64) into a shared-memory ring;
+//   warp 1     MMA      : one elected lane issues tcgen05.mma (M=128, N=BN, K=16, fp32
+//                         accumulate) from shared-memory descriptors into one of two
+//                         accumulators in tensor memory; tcgen05.commit frees ring slots and
+//                         publishes finished accumulators;
+//   warps 2-17 epilogue : tcgen05.ld of the accumulator (warp%4 selects the 32-lane quadrant a
+//                         warp may read, the other two bits a group of columns), bias, rounding
+//                         to the storage type, GELU by table, residual; the result goes to a
+//                         swizzled staging tile and leaves through a TMA store, which writes
+//                         whole lines and clips the ragged edge of the matrix.  The residual
+//                         tile arrives by TMA load into the same staging tile.
+// The double-buffered accumulator lets the epilogue of tile i overlap the products of tile
+// i+1.  Every mbarrier wait is bounded; a wait that runs out records kStatusStageTimeout in
+// the device status word, the roles leave their loops and the CTA frees its tensor memory.
+//
+// The epilogue, not the tensor pipe, bounds this kernel at the model's shapes (K = 64..512,
+// so a 128 x 256 tile needs only 4-32 MMA instructions but 32768 activations); that is why it
+// gets sixteen warps, why per-element work is kept to a table lookup for GELU, and why stores
+// are left to the TMA unit instead of per-lane 16-byte writes to 32 different rows.
+//
+// Rounding mirrors the unfused module sequence: the product plus bias is rounded to the
+// storage type first (what nn.Linear would have written), the activation or residual is then
+// evaluated in fp32 on that rounded value and rounded once more.
+//
+// Building with -DDCNB200_LINEAR_PROFILE adds clock64() timers around the phases of each role
+// (CTA 0 only) and an extra entry point that returns them; it is a tuning aid, off by default.
+#include <cuda.h>
+
+#include <mutex>
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace dcnb200 {
+
+namespace {
+
+constexpr int kBM = 128;        // rows of x per tile == tensor-memory lanes
+constexpr int kBK = 64;         // 64 16-bit elements == 128 bytes == one swizzle span
+#ifndef DCNB200_LINEAR_EPI_WARPS
+#define DCNB200_LINEAR_EPI_WARPS 16
+#endif
+constexpr int kEpiWarps = DCNB200_LINEAR_EPI_WARPS;  // 4 quadrants x column groups
+constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
+constexpr int kUmmaK = 16;          // K of one tcgen05.mma for 16-bit operands
+constexpr int kStagingTile = 4096;  // epilogue staging tile of one warp: 32 rows x (at most) 128 bytes
+constexpr int kBarrierBytes = 512;
+
+// GELU by table.  The activation is applied to a value already rounded to the 16-bit storage
+// type, so there are only 65536 possible inputs; for 2^-12 <= |h| < 8 the result is read from a
+// table that every CTA fills in its prologue with the erf formula, which makes it bit-identical
+// to evaluating erff per element.  Outside that range (about one pre-activation in a thousand
+// even for a freshly initialised network) a warp-uniform branch evaluates the rest: below
+// 2^-12 the Maclaurin series of the normal CDF is exact to fp32 rounding, and from 8 upward
+// GELU(h) is h (or -0 for negative h) in 16-bit precision.
+// Layout: entry [d + sign * kSpan], d = (bits & 0x7fff) - kLo.
+template <typename T> struct GeluLut;
+template <> struct GeluLut<__half> {
+  static constexpr uint32_t kLo = 0x0C00, kSpan = 0x3C00;  // 2^-12 .. 8, 10-bit mantissa (60 KB)
+};
+template <> struct GeluLut<__nv_bfloat16> {
+  static constexpr uint32_t kLo = 0x3980, kSpan = 0x0780;  // 2^-12 .. 8, 7-bit mantissa
+};
+template <typename T, int ACT>
+constexpr int lut_bytes() { return ACT == 1 ? (int)(2 * GeluLut<T>::kSpan * 2 + 1023) / 1024 * 1024 : 0; }
+constexpr int kBiasBytes = kEpiWarps * 64 * 4;  // fp32 bias of each epilogue warp's current 64 columns
+
+// Shared-memory ring depth: as many (x tile + W tile) slots as fit beside staging and table.
+template <typename T, int BN, int ACT>
+constexpr int stages() {
+  constexpr int slot = kBM * kBK * 2 + BN * kBK * 2;
+  constexpr int room = 227 * 1024 - 1024 - kBarrierBytes - kBiasBytes - kEpiWarps * kStagingTile - lut_bytes<T, ACT>();
+  return room / slot > 8 ? 8 : room / slot;
+}
+// Column groups the epilogue warps split a tile into (each at least 32 columns wide).
+template <int BN>
+constexpr int col_groups() { return kEpiWarps / 4 < BN / 32 ? kEpiWarps / 4 : BN / 32; }
+
+struct LinearParams {
+  long long M;
+  int N, K;
+  int m_tiles, n_tiles, k_blocks;
+  const void* bias;      // (N) or null
+  const void* residual;  // (M,N) or null
+  void* y;
+  int* status;
+};
+
+template <typename T, int BN, int ACT>
+constexpr size_t ring_bytes() { return (size_t)stages<T, BN, ACT>() * (kBM * kBK * 2 + BN * kBK * 2); }
+template <typename T, int BN, int ACT>
+constexpr size_t smem_bytes() {
+  return ring_bytes<T, BN, ACT>() + kEpiWarps * kStagingTile + lut_bytes<T, ACT>() + kBiasBytes + 1024 /*alignment slack*/ +
+         kBarrierBytes;
+}
+
+// Columns of one epilogue staging unit: a warp's share of the tile, at most 64 (128 bytes).
+template <int BN>
+constexpr int unit_cols() { return BN / col_groups<BN>() < 64 ? BN / col_groups<BN>() : 64; }
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                           bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread t of the warp receives lane (quadrant*32+t).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 16-bit
+// elements) apart and 128-byte swizzled, as TMA writes it: 8-row groups every 1024 bytes.
+//   bits [0,14) start address >> 4, [16,30) leading byte offset >> 4 (1: unused for swizzled
+//   K-major), [32,46) stride byte offset >> 4 (1024 B between 8-row groups), [46,48) version 1,
+//   [61,64) layout 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
+  uint64_t d = (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor of kind::f16: fp32 accumulator (bits [4,6) = 1), A/B element type at
+// [7,10) and [10,13) (0 fp16, 1 bf16), both operands K-major (bits 15,16 = 0), N>>3 at
+// [17,23), M>>4 at [24,29).
+template <typename T>
+__host__ __device__ constexpr uint32_t instr_desc(int bn) {
+  const uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Two fp32 values rounded (nearest even) into one packed 16-bit pair, and back.
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t u);
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+}
+
+// GELU outside the table's range, for one 16-bit value with bits `hb` and value `hf`.
+template <typename T>
+__device__ __forceinline__ uint32_t gelu_outside_table(uint32_t hb, float hf) {
+  // small |h|: h * Phi(h), Phi(h) = 1/2 + h/sqrt(2 pi) - h^3/(6 sqrt(2 pi)) + O(h^5)
+  const float small_v = hf * fmaf(hf, fmaf(hf * hf, -0.066490380f, 0.39894228f), 0.5f);
+  // |h| >= 8: h for h > 0, -0 for h < 0; NaN and -inf come out as NaN like the erf formula
+  const float big_v = hf * (hf > 0.f ? 1.f : 0.f);
+  return pack2<T>((hb & 0x7FFFu) < GeluLut<T>::kLo ? small_v : big_v, 0.f) & 0xFFFFu;
+}
+// GELU of a packed pair of 16-bit values; see GeluLut.  Must be called by the whole warp.
+template <typename T>
+__device__ __forceinline__ uint32_t gelu_lut2(uint32_t h2, const uint16_t* lut) {
+  constexpr uint32_t kLo = GeluLut<T>::kLo, kSpan = GeluLut<T>::kSpan;
+  const uint32_t x0 = h2 & 0xFFFFu, x1 = h2 >> 16;
+  const uint32_t d0 = (x0 & 0x7FFFu) - kLo, d1 = (x1 & 0x7FFFu) - kLo;
+  uint32_t t0 = lut[min(d0, kSpan - 1) + (x0 >> 15) * kSpan];
+  uint32_t t1 = lut[min(d1, kSpan - 1) + (x1 >> 15) * kSpan];
+  const bool out0 = d0 >= kSpan, out1 = d1 >= kSpan;
+  if (__any_sync(0xffffffffu, out0 | out1)) {
+    const float2 f = unpack2<T>(h2);
+    if (out0) t0 = gelu_outside_table<T>(x0, f.x);
+    if (out1) t1 = gelu_outside_table<T>(x1, f.y);
+  }
+  return t0 | (t1 << 16);
+}
+
+#ifdef DCNB200_LINEAR_PROFILE
+__device__ long long g_lin_prof[16];
+#define PROF_T0() long long _t0 = clock64()
+#define PROF_ADD(slot) do { long long _t1 = clock64(); if (blockIdx.x == 0) prof_acc[slot] += _t1 - _t0; _t0 = _t1; } while (0)
+#else
+#define PROF_T0() do {} while (0)
+#define PROF_ADD(slot) do {} while (0)
+#endif
+
+// ---- kernel ------------------------------------------------------------------------------
+
+template <typename T, int BN, int ACT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+              const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_r,
+              const LinearParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  // 128-byte swizzled tiles must start on a 1024-byte boundary.
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = BN * kBK * 2;
+  unsigned char* ring_a = smem;
+  constexpr int kStages = stages<T, BN, ACT>();
+  constexpr int kCG = col_groups<BN>();
+  unsigned char* ring_b = smem + kStages * kBytesA;
+  unsigned char* staging = smem + ring_bytes<T, BN, ACT>();
+  uint16_t* lut = reinterpret_cast<uint16_t*>(staging + kEpiWarps * kStagingTile);
+  float* bias_f32 = reinterpret_cast<float*>(staging + kEpiWarps * kStagingTile + lut_bytes<T, ACT>());
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpiWarps * kStagingTile + lut_bytes<T, ACT>() + kBiasBytes);
+  uint64_t* full = bars;                  // [kStages] TMA landed
+  uint64_t* empty = bars + kStages;       // [kStages] MMA finished reading
+  uint64_t* acc_full = bars + 2 * kStages;      // [2] accumulator complete
+  uint64_t* acc_empty = bars + 2 * kStages + 2; // [2] accumulator drained by the epilogue
+  uint64_t* res_bars = bars + 2 * kStages + 4;  // [kEpiWarps] residual tile landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bars + kEpiWarps);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two: BN in {32,64,128,256}
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4 * kCG); }
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(&res_bars[w], 1);
+    *abort_flag = 0;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const long long n_tiles_total = (long long)p.m_tiles * p.n_tiles;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+#ifdef DCNB200_LINEAR_PROFILE
+      long long prof_acc[16] = {0};
+#endif
+      PROF_T0();
+      for (long long t = blockIdx.x; t < n_tiles_total && !*abort_flag; t += gridDim.x) {
+        const int mt = (int)(t / p.n_tiles), nt = (int)(t % p.n_tiles);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          PROF_ADD(0);
+          if (!mbar_wait_bounded(&empty[stage], phase ^ 1)) { atomicExch(p.status, kStatusStageTimeout); *abort_flag = 1; break; }
+          PROF_ADD(1);
+          mbar_expect_tx(&full[stage], kBytesA + kBytesB);
+          tma_load_2d(ring_a + stage * kBytesA, &map_x, kb * kBK, mt * kBM, &full[stage]);
+          tma_load_2d(ring_b + stage * kBytesB, &map_w, kb * kBK, nt * BN, &full[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+#ifdef DCNB200_LINEAR_PROFILE
+      if (blockIdx.x == 0) { g_lin_prof[0] = prof_acc[0]; g_lin_prof[1] = prof_acc[1]; }
+#endif
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc<T>(BN);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+#ifdef DCNB200_LINEAR_PROFILE
+      long long prof_acc[16] = {0};
+#endif
+      PROF_T0();
+      for (long long t = blockIdx.x; t < n_tiles_total && !*abort_flag; t += gridDim.x) {
+        PROF_ADD(2);
+        if (!mbar_wait_bounded(&acc_empty[acc], acc_phase ^ 1)) { atomicExch(p.status, kStatusStageTimeout); *abort_flag = 1; break; }
+        PROF_ADD(3);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          PROF_ADD(2);
+          if (!mbar_wait_bounded(&full[stage], phase)) { atomicExch(p.status, kStatusStageTimeout); *abort_flag = 1; break; }
+          PROF_ADD(4);
+          tc_fence_after();
+          const uint64_t da = smem_desc_sw128(ring_a + stage * kBytesA);
+          const uint64_t db = smem_desc_sw128(ring_b + stage * kBytesB);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)  // 32 bytes further along K inside the swizzle span
+            tc_mma_f16(d_tmem, da + (uint64_t)(k * kUmmaK * 2 / 16), db + (uint64_t)(k * kUmmaK * 2 / 16), idesc,
+                       (kb | k) != 0);
+          tc_commit(&empty[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        tc_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+#ifdef DCNB200_LINEAR_PROFILE
+      if (blockIdx.x == 0) { g_lin_prof[2] = prof_acc[2]; g_lin_prof[3] = prof_acc[3]; g_lin_prof[4] = prof_acc[4]; }
+#endif
+    }
+  } else if (warp - 2 < 4 * kCG) {
+    // ---------------------------------------------------------------- epilogue
+    // Each lane owns one accumulator row (that is how tensor memory is read).  It applies bias,
+    // rounding, activation and residual and parks 16-byte pieces in a staging tile laid out with
+    // the TMA swizzle; one lane then hands the tile to a TMA store, which writes whole lines
+    // and clips rows and columns beyond the matrix.  The residual tile arrives the same way
+    // (TMA load into the staging tile, consumed in place).  Two staging tiles per warp let the
+    // store of one unit overlap the arithmetic of the next.
+    const int quad = warp & 3;              // tensor-memory lanes [32*quad, 32*quad+32)
+    const int group = (warp - 2) >> 2;      // which column group of the tile
+    constexpr int kColsPerWarp = BN / kCG;
+    constexpr int UW = unit_cols<BN>();     // columns per staging unit (32 or 64)
+    constexpr int RB = UW * 2;        // bytes per staged row (64 or 128) == swizzle span
+    constexpr int CPR = RB / 16;      // 16-byte pieces per row
+    constexpr int RPW = 128 / RB;     // rows per 128-byte bank window
+    unsigned char* buf = staging + (warp - 2) * kStagingTile;
+    uint64_t* res_bar = &res_bars[warp - 2];
+    float* my_bias = bias_f32 + (warp - 2) * 64;
+    const T* bias = static_cast<const T*>(p.bias);
+    const bool has_res = p.residual != nullptr;
+    int acc = 0;
+    uint32_t acc_phase = 0, unit = 0;
+    if (ACT == 1) {
+      // Fill the GELU table (epilogue warps only; the pipeline fills meanwhile).
+      // One erff serves both signs: erff is odd, so 1 + erff(-z) == 1 - erff(z) exactly.
+      for (uint32_t d = threadIdx.x - 64; d < GeluLut<T>::kSpan; d += 32 * 4 * kCG) {
+        const float x = unpack2<T>(GeluLut<T>::kLo + d).x;
+        const float e = erff(x * 0.70710678118654752440f);
+        lut[d] = (uint16_t)(pack2<T>(0.5f * x * (1.0f + e), 0.f) & 0xFFFFu);
+        lut[d + GeluLut<T>::kSpan] = (uint16_t)(pack2<T>(0.5f * -x * (1.0f - e), 0.f) & 0xFFFFu);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * 4 * kCG) : "memory");
+    }
+#ifdef DCNB200_LINEAR_PROFILE
+    long long prof_acc[16] = {0};
+#endif
+    PROF_T0();
+    for (long long t = blockIdx.x; t < n_tiles_total && !*abort_flag; t += gridDim.x) {
+      const int mt = (int)(t / p.n_tiles), nt = (int)(t % p.n_tiles);
+      PROF_ADD(5);
+      if (!mbar_wait_bounded(&acc_full[acc], acc_phase)) {
+        if (lane == 0) { atomicExch(p.status, kStatusStageTimeout); *abort_flag = 1; }
+        break;
+      }
+      tc_fence_after();
+      PROF_ADD(6);
+      const int row0 = mt * kBM + quad * 32;
+      const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + group * kColsPerWarp);
+#pragma unroll 1
+      for (int c = 0; c < kColsPerWarp; c += UW, ++unit) {
+        const int col0 = nt * BN + group * kColsPerWarp + c;
+        if (col0 >= p.N) break;  // warp-uniform
+        // The previous store read this tile; it must be done before we overwrite it.
+        if (lane == 0) {
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          if (has_res) {
+            mbar_expect_tx(res_bar, 32 * RB);
+            tma_load_2d(buf, &map_r, col0, row0, res_bar);
+          }
+        }
+        // Accumulator columns are fetched 32 at a time (32 registers); the first fetch is in
+        // flight while the warp stages this unit's bias as fp32 (two columns per lane, zero
+        // where there is none) so that the per-row loop reads it with 16-byte shared loads.
+        uint32_t v[32];
+        tmem_ld_32x32(taddr0 + (uint32_t)c, v);
+#pragma unroll
+        for (int q = lane * 2; q < UW; q += 64) {
+          const int col = col0 + q;
+          float2 b = make_float2(0.f, 0.f);
+          if (bias != nullptr && col < p.N) b = unpack2<T>(__ldg(reinterpret_cast<const uint32_t*>(bias + col)));
+          *reinterpret_cast<float2*>(my_bias + q) = b;
+        }
+        __syncwarp();
+        if (has_res && !mbar_wait_bounded(res_bar, unit & 1)) {
+          if (lane == 0) { atomicExch(p.status, kStatusStageTimeout); *abort_flag = 1; }
+        }
+#pragma unroll
+        for (int cc = 0; cc < UW; cc += 32) {
+          if (cc > 0) tmem_ld_32x32(taddr0 + (uint32_t)(c + cc), v);
+          tmem_ld_wait();
+          PROF_ADD(7);
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            const float4 bA = *reinterpret_cast<const float4*>(my_bias + cc + j);
+            const float4 bB = *reinterpret_cast<const float4*>(my_bias + cc + j + 4);
+            const float b8[8] = {bA.x, bA.y, bA.z, bA.w, bB.x, bB.y, bB.z, bB.w};
+            uint4* slot = reinterpret_cast<uint4*>(buf + lane * RB + ((((cc + j) >> 3) ^ ((lane / RPW) % CPR)) << 4));
+            uint32_t r4[4] = {0u, 0u, 0u, 0u};
+            if (has_res) { const uint4 r = *slot; r4[0] = r.x; r4[1] = r.y; r4[2] = r.z; r4[3] = r.w; }
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              float f0 = __uint_as_float(v[j + e]), f1 = __uint_as_float(v[j + e + 1]);
+              f0 += b8[e]; f1 += b8[e + 1];
+              uint32_t h2 = pack2<T>(f0, f1);  // rounded to storage, as nn.Linear would write it
+              if (ACT == 1) h2 = gelu_lut2<T>(h2, lut);
+              if (has_res) {
+                const float2 h = unpack2<T>(h2);
+                const float2 r = unpack2<T>(r4[e >> 1]);
+                h2 = pack2<T>(h.x + r.x, h.y + r.y);
+              }
+              o[e >> 1] = h2;
+            }
+            *slot = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        PROF_ADD(8);
+        if (lane == 0) {
+          tma_store_2d(&map_y, buf, col0, row0);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        PROF_ADD(9);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+#ifdef DCNB200_LINEAR_PROFILE
+    if (blockIdx.x == 0 && warp == 2 && lane == 0)
+      for (int i = 5; i < 10; ++i) g_lin_prof[i] = prof_acc[i];
+#endif
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 2-D map over a row-major (rows, cols) 16-bit matrix with a (box_rows x box_cols) box whose
+// row of box_cols*2 bytes is exactly one swizzle span (64 or 128 bytes); out-of-range elements
+// read as zero and are not written.
+bool make_map(CUtensorMap* m, int dtype, const void* base, long long rows, int cols, int box_rows, int box_cols) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapSwizzle sw = box_cols * 2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  return enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct LinearArgs {
+  int dtype;
+  const void* x; const void* w; const void* residual; void* y;
+};
+
+template <typename T, int BN, int ACT>
+cudaError_t launch_act(const LinearArgs& a, LinearParams p, int sms, cudaStream_t stream) {
+  static std::once_flag once[64];
+  static cudaError_t attr_err[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev = dev < 0 || dev >= 64 ? 0 : dev;
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(linear_kernel<T, BN, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem_bytes<T, BN, ACT>());
+  });
+  if (attr_err[dev] != cudaSuccess) return attr_err[dev];
+  CUtensorMap mx, mw, my, mr;
+  constexpr int UW = unit_cols<BN>();
+  if (!make_map(&mx, a.dtype, a.x, p.M, p.K, kBM, kBK) || !make_map(&mw, a.dtype, a.w, p.N, p.K, BN, kBK) ||
+      !make_map(&my, a.dtype, a.y, p.M, p.N, 32, UW) ||
+      !make_map(&mr, a.dtype, a.residual ? a.residual : a.y, p.M, p.N, 32, UW))
+    return cudaErrorNotSupported;
+  p.n_tiles = (p.N + BN - 1) / BN;
+  const long long tiles = (long long)p.m_tiles * p.n_tiles;
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  linear_kernel<T, BN, ACT><<<grid, kGemmThreads, smem_bytes<T, BN, ACT>(), stream>>>(mx, mw, my, mr, p);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_bn(int bn, int act, const LinearArgs& a, const LinearParams& p, int sms, cudaStream_t stream) {
+  if (act == 1) {
+    if (bn == 256) return launch_act<T, 256, 1>(a, p, sms, stream);
+    if (bn == 128) return launch_act<T, 128, 1>(a, p, sms, stream);
+    return launch_act<T, 64, 1>(a, p, sms, stream);
+  }
+  if (bn == 256) return launch_act<T, 256, 0>(a, p, sms, stream);
+  if (bn == 128) return launch_act<T, 128, 0>(a, p, sms, stream);
+  return launch_act<T, 64, 0>(a, p, sms, stream);
+}
+
+}  // namespace
+
+// dtype: 1 fp16, 2 bf16.  Returns cudaErrorNotSupported when the driver lacks tensor maps.
+cudaError_t launch_linear_fwd(int dtype, const void* x, const void* w, const void* bias, const void* residual,
+                              void* y, long long M, int N, int K, int act, int sms, int* status,
+                              cudaStream_t stream) {
+  // Tile width: the widest of 256/128/64 that N fills, unless a narrower one wastes less of the
+  // last wave of CTAs (cost model: waves x (columns + fixed per-tile overhead)).
+  const int m_tiles = (int)((M + kBM - 1) / kBM);
+  int bn = 64;
+  double best = 1e30;
+  for (int cand = 256; cand >= 64; cand /= 2) {
+    if (cand > 64 && N <= cand / 2) continue;
+    // a ring too shallow to cover the TMA latency of a multi-block K loop is not worth the width
+    const int depth = cand == 256 ? (act ? stages<__half, 256, 1>() : stages<__half, 256, 0>())
+                                  : (cand == 128 ? (act ? stages<__half, 128, 1>() : stages<__half, 128, 0>()) : 8);
+    if (cand > 64 && depth < 3 && (K + kBK - 1) / kBK > depth) continue;
+    const long long tiles = (long long)m_tiles * ((N + cand - 1) / cand);
+    const double cost = (double)((tiles + sms - 1) / sms) * (cand + 48);
+    if (cost < best * 0.98) { best = cost; bn = cand; }
+  }
+  LinearParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.m_tiles = (int)((M + kBM - 1) / kBM);
+  p.n_tiles = 0;
+  p.k_blocks = (K + kBK - 1) / kBK;
+  p.bias = bias; p.residual = residual; p.y = y; p.status = status;
+  const LinearArgs a{dtype, x, w, residual, y};
+  if (dtype == 1) return launch_bn<__half>(bn, act, a, p, sms, stream);
+  return launch_bn<__nv_bfloat16>(bn, act, a, p, sms, stream);
+}
+
+}  // namespace dcnb200
+
+#ifdef DCNB200_LINEAR_PROFILE
+extern "C" int dcnv4b200_linear_profile(long long* out16) {
+  return (int)cudaMemcpyFromSymbol(out16, dcnb200::g_lin_prof, sizeof(long long) * 16);
+}
+#endif

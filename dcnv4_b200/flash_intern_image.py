@@ -142,8 +142,14 @@ class MLPLayer(nn.Module):
         self.fc2 = nn.Linear(hidden_features, out_features, bias=mlp_fc2_bias)
         self.drop = nn.Dropout(drop)
 
-    def forward(self, x, shape=None):
-        return self.drop(self.fc2(self.drop(self.act(self.fc1(x)))))
+    def forward(self, x, shape=None, residual=None):
+        """fc2(act(fc1(x))) [+ residual]; at inference GELU and the residual addition are fused
+        into the two matrix products (dropout is the identity there)."""
+        if isinstance(self.act, nn.GELU) and self.act.approximate == "none" and not (self.training and self.drop.p > 0):
+            h = ops.linear_module_forward(x, self.fc1, None, "gelu")
+            return ops.linear_module_forward(h, self.fc2, residual)
+        y = self.drop(self.fc2(self.drop(self.act(self.fc1(x)))))
+        return y if residual is None else residual + y
 
 
 class InternImageLayer(nn.Module):
@@ -173,6 +179,10 @@ class InternImageLayer(nn.Module):
             x = x + self.drop_path(self.gamma1 * a if self.layer_scale else a)
             m = self.norm2(self.mlp(x, shape))
             x = x + self.drop_path(self.gamma2 * m if self.layer_scale else m)
+        elif not self.layer_scale and (not self.training or isinstance(self.drop_path, nn.Identity)):
+            # plain residual blocks: the additions ride on the output projection and on fc2
+            x = self.dcn(self.norm1(x), shape, residual=x)
+            x = self.mlp(self.norm2(x), shape, residual=x)
         else:
             a = self.dcn(self.norm1(x), shape)
             x = x + self.drop_path(self.gamma1 * a if self.layer_scale else a)

@@ -12,6 +12,7 @@ import torch.nn.functional as F
 from torch import nn
 from torch.nn.init import constant_, xavier_uniform_
 
+from .. import ops
 from ..functions import DCNv4Function
 
 
@@ -73,9 +74,11 @@ class DCNv4(nn.Module):
             if self.output_proj.bias is not None:
                 constant_(self.output_proj.bias.data, 0.)
 
-    def forward(self, input, shape=None):
+    def forward(self, input, shape=None, residual=None):
         """input (N, L, C) with L = H*W; `shape` = (H, W) when the map is not square.
-        Returns (N, L, C)."""
+        Returns (N, L, C).  `residual` (N, L, C), an extension over the reference signature,
+        is added to the result; at inference the addition is fused into the output
+        projection."""
         N, L, C = input.shape
         if shape is not None:
             H, W = shape
@@ -107,5 +110,5 @@ class DCNv4(nn.Module):
 
         x = x.view(N, L, -1)
         if not self.without_pointwise:
-            x = self.output_proj(x)
-        return x
+            return ops.linear_module_forward(x, self.output_proj, residual)
+        return x if residual is None else residual + x

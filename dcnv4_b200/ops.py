@@ -6,7 +6,7 @@ and call the library on the current CUDA stream.
 """
 from __future__ import annotations
 
-from typing import List, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -196,6 +196,70 @@ def layer_norm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
         return False
     return weight is not None and weight.is_cuda and weight.dtype in (torch.float32, x.dtype) \
         and x.data_ptr() % 16 == 0
+
+
+def linear_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                   residual: Optional[torch.Tensor] = None, activation: str = "none") -> torch.Tensor:
+    """y = act(x @ weight.T + bias) [+ residual] in one tensor-core kernel (forward only; no
+    autograd; fp16 / bf16).  `activation` is "none" or "gelu" (erf form, as nn.GELU()).  Raises
+    ValueError / RuntimeError for inputs the kernel does not cover -- callers that want a
+    fallback check `linear_supported` first."""
+    _check_tensor(x, "input")
+    _check_tensor(weight, "weight")
+    if activation not in ("none", "gelu"):
+        raise ValueError("activation must be 'none' or 'gelu'")
+    N, K = weight.shape
+    if x.shape[-1] != K or weight.dtype != x.dtype:
+        raise RuntimeError("weight must be (out_features, in_features) in the dtype of the input")
+    for t, name in ((bias, "bias"), (residual, "residual")):
+        if t is not None:
+            _check_tensor(t, name)
+            if t.dtype != x.dtype:
+                raise RuntimeError(f"{name} must have the dtype of the input")
+    M = x.numel() // max(K, 1)
+    if bias is not None and bias.numel() != N:
+        raise RuntimeError("bias must have out_features elements")
+    if residual is not None and residual.numel() != M * N:
+        raise RuntimeError("residual must have the shape of the output")
+    y = torch.empty(x.shape[:-1] + (N,), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().dcnv4b200_linear_fwd(x.data_ptr(), weight.data_ptr(),
+                                             bias.data_ptr() if bias is not None else None,
+                                             residual.data_ptr() if residual is not None else None,
+                                             y.data_ptr(), _code(x), M, N, K, 1 if activation == "gelu" else 0,
+                                             _stream(x))
+    _lib.check(rc, "linear_forward")
+    return y
+
+
+def linear_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """True when `linear_forward` covers this input (dtype, size, layout)."""
+    if not (x.is_cuda and x.is_contiguous() and x.dtype in (torch.float16, torch.bfloat16) and x.numel() > 0):
+        return False
+    if weight is None or not weight.is_cuda or weight.dtype != x.dtype or not weight.is_contiguous():
+        return False
+    N, K = weight.shape
+    return N % 8 == 0 and K % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+
+
+FUSED_LINEAR = True  # benchmarks turn this off to time the stock nn.Linear / GELU / add kernels
+
+
+def linear_module_forward(x: torch.Tensor, lin: "torch.nn.Linear", residual: Optional[torch.Tensor] = None,
+                          activation: str = "none") -> torch.Tensor:
+    """`residual + act(lin(x))` for an nn.Linear: one fused tensor-core kernel when autograd
+    is not needed and the kernel covers the input, else the stock PyTorch operations (same
+    result up to fp rounding: the fused kernel rounds at the same points)."""
+    needs_grad = torch.is_grad_enabled() and (x.requires_grad or lin.weight.requires_grad)
+    if (FUSED_LINEAR and not needs_grad and not torch.is_autocast_enabled() and linear_supported(x, lin.weight)
+            and (lin.bias is None or (lin.bias.dtype == x.dtype and lin.bias.data_ptr() % 16 == 0))
+            and (residual is None or (residual.dtype == x.dtype and residual.is_contiguous()
+                                      and residual.data_ptr() % 16 == 0))):
+        return linear_forward(x, lin.weight, lin.bias, residual, activation)
+    y = torch.nn.functional.linear(x, lin.weight, lin.bias)
+    if activation == "gelu":
+        y = torch.nn.functional.gelu(y)
+    return y if residual is None else residual + y
 
 
 def dcnv4_corners(p_offset, H, W, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, dilation_h,

@@ -159,6 +159,24 @@ int dcnv4b200_layernorm_fwd(const void* x, const void* gamma, const void* beta, 
                             int param_dtype, long long rows, int C, float eps, void* stream);
 
 /*
+ * Linear layer with a fused epilogue, inference only, on the tcgen05 tensor cores:
+ *     t = x . weight^T + bias            rounded to `dtype` (what nn.Linear would store)
+ *     t = GELU(t)                        if activation == DCNV4B200_ACT_GELU (erf form)
+ *     y = t + residual                   if residual != NULL
+ * The reference runs these steps as separate kernels around every DCNv4 operator: nn.Linear,
+ * nn.GELU and the residual additions of MLPLayer / InternImageLayer
+ * (classification/models/flash_intern_image.py:308-341, :414-432); it has no fused kernel.
+ *   x (M,K), weight (N,K) as nn.Linear stores it, bias (N) or NULL, residual (M,N) or NULL,
+ *   y (M,N); all row-major and contiguous in `dtype`, which must be fp16 or bf16
+ *   (DCNV4B200_ERR_DTYPE otherwise).  N and K must be multiples of 8 (_ERR_CHANNELS), every
+ *   pointer 16-byte aligned.  y may alias residual; it must not alias x.
+ */
+#define DCNV4B200_ACT_NONE 0
+#define DCNV4B200_ACT_GELU 1
+int dcnv4b200_linear_fwd(const void* x, const void* weight, const void* bias, const void* residual, void* y,
+                         int dtype, long long M, int N, int K, int activation, void* stream);
+
+/*
  * Read and clear the current device's kernel status word (0 = no kernel ever gave up on a
  * bounded wait for its staged tile).  Synchronises the device; meant for tests and
  * post-mortems, not for the hot path.  No counterpart in the reference.

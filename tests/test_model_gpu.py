@@ -44,6 +44,8 @@ def test_every_dcn_layer_of_a_tiny_model_matches_the_oracle():
             core = cref.dcnv4_forward(v.cpu(), om.cpu(), 3, 3, 1, 1, 1, 1, 1, 1, mod.group, mod.group_channels,
                                       mod.offset_scale, 0)
             ref = mod.output_proj(core.to(DEV).float().reshape(N, L, C))
+            if kwargs.get("residual") is not None:      # the block lets the module add its skip path
+                ref = kwargs["residual"] + ref
         torch.testing.assert_close(out, ref, rtol=1e-3, atol=1e-4)
 
 
