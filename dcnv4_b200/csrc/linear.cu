@@ -225,21 +225,33 @@ __device__ __forceinline__ uint32_t gelu_outside_table(uint32_t hb, float hf) {
   const float big_v = hf * (hf > 0.f ? 1.f : 0.f);
   return pack2<T>((hb & 0x7FFFu) < GeluLut<T>::kLo ? small_v : big_v, 0.f) & 0xFFFFu;
 }
-// GELU of a packed pair of 16-bit values; see GeluLut.  Must be called by the whole warp.
+// GELU of eight 16-bit values packed in four registers, in place; see GeluLut.  Must be called
+// by the whole warp: all table reads are issued first, then ONE vote decides whether any lane
+// holds a value outside the table, so the common path has no branch between the lookups.
 template <typename T>
-__device__ __forceinline__ uint32_t gelu_lut2(uint32_t h2, const uint16_t* lut) {
+__device__ __forceinline__ void gelu_lut8(uint32_t (&h)[4], const uint16_t* lut) {
   constexpr uint32_t kLo = GeluLut<T>::kLo, kSpan = GeluLut<T>::kSpan;
-  const uint32_t x0 = h2 & 0xFFFFu, x1 = h2 >> 16;
-  const uint32_t d0 = (x0 & 0x7FFFu) - kLo, d1 = (x1 & 0x7FFFu) - kLo;
-  uint32_t t0 = lut[min(d0, kSpan - 1) + (x0 >> 15) * kSpan];
-  uint32_t t1 = lut[min(d1, kSpan - 1) + (x1 >> 15) * kSpan];
-  const bool out0 = d0 >= kSpan, out1 = d1 >= kSpan;
-  if (__any_sync(0xffffffffu, out0 | out1)) {
-    const float2 f = unpack2<T>(h2);
-    if (out0) t0 = gelu_outside_table<T>(x0, f.x);
-    if (out1) t1 = gelu_outside_table<T>(x1, f.y);
+  uint32_t t[8];
+  bool any_out = false;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t x0 = h[i] & 0xFFFFu, x1 = h[i] >> 16;
+    const uint32_t d0 = (x0 & 0x7FFFu) - kLo, d1 = (x1 & 0x7FFFu) - kLo;
+    t[2 * i] = lut[min(d0, kSpan - 1) + (x0 >> 15) * kSpan];
+    t[2 * i + 1] = lut[min(d1, kSpan - 1) + (x1 >> 15) * kSpan];
+    any_out |= (d0 >= kSpan) | (d1 >= kSpan);
   }
-  return t0 | (t1 << 16);
+  if (__any_sync(0xffffffffu, any_out)) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t x0 = h[i] & 0xFFFFu, x1 = h[i] >> 16;
+      const float2 f = unpack2<T>(h[i]);
+      if ((x0 & 0x7FFFu) - kLo >= kSpan) t[2 * i] = gelu_outside_table<T>(x0, f.x);
+      if ((x1 & 0x7FFFu) - kLo >= kSpan) t[2 * i + 1] = gelu_outside_table<T>(x1, f.y);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = t[2 * i] | (t[2 * i + 1] << 16);
 }
 
 #ifdef DCNB200_LINEAR_PROFILE
@@ -452,17 +464,16 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             if (has_res) { const uint4 r = *slot; r4[0] = r.x; r4[1] = r.y; r4[2] = r.z; r4[3] = r.w; }
             uint32_t o[4];
 #pragma unroll
-            for (int e = 0; e < 8; e += 2) {
-              float f0 = __uint_as_float(v[j + e]), f1 = __uint_as_float(v[j + e + 1]);
-              f0 += b8[e]; f1 += b8[e + 1];
-              uint32_t h2 = pack2<T>(f0, f1);  // rounded to storage, as nn.Linear would write it
-              if (ACT == 1) h2 = gelu_lut2<T>(h2, lut);
-              if (has_res) {
-                const float2 h = unpack2<T>(h2);
-                const float2 r = unpack2<T>(r4[e >> 1]);
-                h2 = pack2<T>(h.x + r.x, h.y + r.y);
+            for (int e = 0; e < 8; e += 2)  // rounded to storage, as nn.Linear would write it
+              o[e >> 1] = pack2<T>(__uint_as_float(v[j + e]) + b8[e], __uint_as_float(v[j + e + 1]) + b8[e + 1]);
+            if (ACT == 1) gelu_lut8<T>(o, lut);
+            if (has_res) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float2 h = unpack2<T>(o[q]);
+                const float2 r = unpack2<T>(r4[q]);
+                o[q] = pack2<T>(h.x + r.x, h.y + r.y);
               }
-              o[e >> 1] = h2;
             }
             *slot = make_uint4(o[0], o[1], o[2], o[3]);
           }

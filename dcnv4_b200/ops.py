@@ -243,6 +243,10 @@ def linear_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 FUSED_LINEAR = True  # benchmarks turn this off to time the stock nn.Linear / GELU / add kernels
+# The fused kernel streams both operands through one SM's shared memory (no 2-CTA tiles), which
+# bounds long reductions by L2 bandwidth: measured against cuBLAS + separate element-wise kernels
+# it wins up to K = 1024 and loses at K = 2048 (FlashInternImage-T stage-4 fc2: 45 vs 36 us).
+FUSED_LINEAR_MAX_K = 1024
 
 
 def linear_module_forward(x: torch.Tensor, lin: "torch.nn.Linear", residual: Optional[torch.Tensor] = None,
@@ -252,6 +256,7 @@ def linear_module_forward(x: torch.Tensor, lin: "torch.nn.Linear", residual: Opt
     result up to fp rounding: the fused kernel rounds at the same points)."""
     needs_grad = torch.is_grad_enabled() and (x.requires_grad or lin.weight.requires_grad)
     if (FUSED_LINEAR and not needs_grad and not torch.is_autocast_enabled() and linear_supported(x, lin.weight)
+            and lin.in_features <= FUSED_LINEAR_MAX_K
             and (lin.bias is None or (lin.bias.dtype == x.dtype and lin.bias.data_ptr() % 16 == 0))
             and (residual is None or (residual.dtype == x.dtype and residual.is_contiguous()
                                       and residual.data_ptr() % 16 == 0))):
