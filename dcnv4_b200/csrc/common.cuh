@@ -335,6 +335,36 @@ __device__ __forceinline__ void wait_stage(uint64_t* bar, uint32_t parity, int* 
   if (!mbar_wait_bounded(bar, parity)) atomicExch(status, kStatusStageTimeout);
 }
 
+// ------------------------------------------------------ programmatic dependent launch
+//
+// The inference-path kernels (LayerNorm, Linear, DCNv4 forward) are launched so that their
+// prologue -- barrier set-up, tensor-memory allocation, table fill -- may start while the
+// previous kernel of the stream is still draining.  pdl_wait() blocks until that kernel has
+// completed and its writes are visible; it must precede the first access to global memory that
+// another kernel may have written and every write to global memory.  pdl_trigger() lets the
+// next kernel's prologue start.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#ifndef DCNB200_PDL
+#define DCNB200_PDL 1
+#endif
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = DCNB200_PDL ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // --------------------------------------------------------------------------- parameters
 
 struct DcnParams {

@@ -64,6 +64,8 @@ dcnv4_fwd_kernel(const T* __restrict__ value, const T* __restrict__ om, T* __res
   const int share = n_tiles / (int)gridDim.x, extra = n_tiles % (int)gridDim.x;
   const int tile_begin = (int)blockIdx.x * share + min((int)blockIdx.x, extra);
   const int tile_end = tile_begin + share + ((int)blockIdx.x < extra ? 1 : 0);
+  pdl_trigger();
+  pdl_wait();  // value and offset_mask are the previous kernels' outputs
   if (threadIdx.x == 0 && tile_begin < tile_end) issue(tile_begin, 0);
 
   const int cw = (p.dw * (kw - 1)) >> 1, ch = (p.dh * (kh - 1)) >> 1;
@@ -181,8 +183,7 @@ static cudaError_t launch_v(const T* value, const T* om, T* out, const DcnParams
   const long long n_tiles = (long long)p.N * p.tiles_x * p.tiles_y;
   const long long want = (long long)p.sm_count * per_sm;
   const int grid = (int)(n_tiles < want ? n_tiles : want);
-  kern<<<grid, kThreads, smem, s>>>(value, om, out, p, status);
-  return cudaGetLastError();
+  return launch_overlapped(kern, dim3((unsigned)grid), dim3(kThreads), smem, s, value, om, out, p, status);
 }
 
 template <typename T>

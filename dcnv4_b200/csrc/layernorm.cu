@@ -40,6 +40,8 @@ layernorm_fwd_kernel(const T* __restrict__ x, const P* __restrict__ gamma, const
     }
   }
 
+  pdl_trigger();
+  pdl_wait();  // x may be the previous kernel's output
   for (long long r0 = warp * rows_per_warp; r0 < rows; r0 += n_warps * rows_per_warp) {
     const long long row = r0 + lane / lpr;
     const bool live = row < rows;
@@ -103,7 +105,7 @@ static cudaError_t launch_tp(const T* x, const P* gamma, const P* beta, T* y, lo
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
 #define LN_CASE(NVV) \
-  case NVV: layernorm_fwd_kernel<T, P, NVV><<<(int)blocks, 256, 0, s>>>(x, gamma, beta, y, rows, C, lpr, eps); break;
+  case NVV: return launch_overlapped(layernorm_fwd_kernel<T, P, NVV>, dim3((unsigned)blocks), dim3(256), 0, s, x, gamma, beta, y, rows, C, lpr, eps);
   switch (nv) {
     LN_CASE(1) LN_CASE(2) LN_CASE(3) LN_CASE(4) LN_CASE(5) LN_CASE(6) LN_CASE(7) LN_CASE(8)
     default: return cudaErrorInvalidValue;

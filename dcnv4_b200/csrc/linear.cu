@@ -308,6 +308,7 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
 
   const long long n_tiles_total = (long long)p.m_tiles * p.n_tiles;
 
@@ -316,6 +317,7 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      pdl_wait();  // x may be the previous kernel's output
 #ifdef DCNB200_LINEAR_PROFILE
       long long prof_acc[16] = {0};
 #endif
@@ -406,6 +408,7 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       }
       asm volatile("bar.sync 1, %0;" ::"n"(32 * 4 * kCG) : "memory");
     }
+    pdl_wait();  // residual may be the previous kernel's output; y may be read by it
 #ifdef DCNB200_LINEAR_PROFILE
     long long prof_acc[16] = {0};
 #endif
@@ -568,8 +571,8 @@ cudaError_t launch_act(const LinearArgs& a, LinearParams p, int sms, cudaStream_
   p.n_tiles = (p.N + BN - 1) / BN;
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   const int grid = (int)(tiles < sms ? tiles : sms);
-  linear_kernel<T, BN, ACT><<<grid, kGemmThreads, smem_bytes<T, BN, ACT>(), stream>>>(mx, mw, my, mr, p);
-  return cudaGetLastError();
+  return launch_overlapped(linear_kernel<T, BN, ACT>, dim3((unsigned)grid), dim3(kGemmThreads),
+                           smem_bytes<T, BN, ACT>(), stream, mx, mw, my, mr, p);
 }
 
 template <typename T>
