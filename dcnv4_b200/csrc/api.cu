@@ -414,6 +414,26 @@ int dcnv4b200_linear_fwd(const void* x, const void* weight, const void* bias, co
                                 static_cast<cudaStream_t>(stream));
 }
 
+int dcnv4b200_linear_ln_fwd(const void* x, const void* weight, const void* bias, const void* residual, void* y,
+                            const void* gamma, const void* beta, float eps, void* z, int dtype, long long M,
+                            int N, int K, void* stream) {
+  if (!x || !weight || !y || !gamma || !beta || !z) return DCNV4B200_ERR_NULL;
+  if (dtype != DCNV4B200_F16 && dtype != DCNV4B200_BF16) return DCNV4B200_ERR_DTYPE;
+  if (M < 0 || N <= 0 || K <= 0) return DCNV4B200_ERR_SHAPE;
+  if (N % 32 != 0 || K % 8 != 0) return DCNV4B200_ERR_CHANNELS;
+  if (N > 256) return DCNV4B200_ERR_UNSUPPORTED;  // a row has to fit one tile of the kernel
+  if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || !aligned16(z) || !aligned16(bias) ||
+      !aligned16(residual) || !aligned16(gamma) || !aligned16(beta))
+    return DCNV4B200_ERR_ALIGN;
+  if (M >= (1LL << 31)) return DCNV4B200_ERR_TOO_LARGE;
+  if (M == 0) return 0;
+  int* status = nullptr;
+  int sms = 1;
+  if (int rc = status_ptr(&status, &sms)) return rc;
+  return (int)launch_linear_fwd(dtype, x, weight, bias, residual, y, M, N, K, 2, sms, status,
+                                static_cast<cudaStream_t>(stream), gamma, beta, eps, z);
+}
+
 int dcnv4b200_device_status(int* status_out) {
   if (!status_out) return DCNV4B200_ERR_NULL;
   int* status = nullptr;

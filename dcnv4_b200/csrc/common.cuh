@@ -444,7 +444,8 @@ int layernorm_max_channels(int dtype);
 // y = epilogue(x . W^T + bias) on the tensor cores (linear.cu); dtype 1 fp16 / 2 bf16.
 cudaError_t launch_linear_fwd(int dtype, const void* x, const void* w, const void* bias, const void* residual,
                               void* y, long long M, int N, int K, int act, int sms, int* status,
-                              cudaStream_t stream);
+                              cudaStream_t stream, const void* gamma = nullptr, const void* beta = nullptr,
+                              float eps = 0.f, void* z = nullptr);
 
 size_t dcnv4_fwd_smem(const DcnParams& p, int elem);
 size_t dcnv4_bwd_smem(const DcnParams& p, int elem);

@@ -76,13 +76,16 @@ template <> struct GeluLut<__nv_bfloat16> {
 };
 template <typename T, int ACT>
 constexpr int lut_bytes() { return ACT == 1 ? (int)(2 * GeluLut<T>::kSpan * 2 + 1023) / 1024 * 1024 : 0; }
-constexpr int kBiasBytes = kEpiWarps * 64 * 4;  // fp32 bias of each epilogue warp's current 64 columns
+// fp32 bias, gamma and beta of each epilogue warp's current 64 columns, then two arrays of
+// per-row partial sums (one float per epilogue thread) for the LayerNorm epilogue
+template <int ACT>
+constexpr int bias_bytes() { return ACT == 2 ? kEpiWarps * 64 * 4 * 3 + 2 * kEpiWarps * 32 * 4 : kEpiWarps * 64 * 4; }
 
 // Shared-memory ring depth: as many (x tile + W tile) slots as fit beside staging and table.
 template <typename T, int BN, int ACT>
 constexpr int stages() {
   constexpr int slot = kBM * kBK * 2 + BN * kBK * 2;
-  constexpr int room = 227 * 1024 - 1024 - kBarrierBytes - kBiasBytes - kEpiWarps * kStagingTile - lut_bytes<T, ACT>();
+  constexpr int room = 227 * 1024 - 1024 - kBarrierBytes - bias_bytes<ACT>() - kEpiWarps * kStagingTile - lut_bytes<T, ACT>();
   return room / slot > 8 ? 8 : room / slot;
 }
 // Column groups the epilogue warps split a tile into (each at least 32 columns wide).
@@ -95,6 +98,9 @@ struct LinearParams {
   int m_tiles, n_tiles, k_blocks;
   const void* bias;      // (N) or null
   const void* residual;  // (M,N) or null
+  const void* gamma;     // LayerNorm epilogue (ACT == 2): weight, bias (N), eps
+  const void* beta;
+  float eps;
   void* y;
   int* status;
 };
@@ -103,7 +109,7 @@ template <typename T, int BN, int ACT>
 constexpr size_t ring_bytes() { return (size_t)stages<T, BN, ACT>() * (kBM * kBK * 2 + BN * kBK * 2); }
 template <typename T, int BN, int ACT>
 constexpr size_t smem_bytes() {
-  return ring_bytes<T, BN, ACT>() + kEpiWarps * kStagingTile + lut_bytes<T, ACT>() + kBiasBytes + 1024 /*alignment slack*/ +
+  return ring_bytes<T, BN, ACT>() + kEpiWarps * kStagingTile + lut_bytes<T, ACT>() + bias_bytes<ACT>() + 1024 /*alignment slack*/ +
          kBarrierBytes;
 }
 
@@ -118,6 +124,11 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
+}
+// Ask the TMA unit to bring a box into L2 (no shared memory, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1)
+               : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -188,15 +199,6 @@ __host__ __device__ constexpr uint32_t instr_desc(int bn) {
   const uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
-
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
-
-template <typename T> __device__ __forceinline__ float to_f(T v);
-template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
-template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-template <typename T> __device__ __forceinline__ T from_f(float v);
-template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
-template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 // Two fp32 values rounded (nearest even) into one packed 16-bit pair, and back.
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -269,7 +271,7 @@ template <typename T, int BN, int ACT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
               const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_r,
-              const LinearParams p) {
+              const __grid_constant__ CUtensorMap map_z, const LinearParams p) {
   extern __shared__ unsigned char smem_raw[];
   // 128-byte swizzled tiles must start on a 1024-byte boundary.
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -281,13 +283,14 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   unsigned char* staging = smem + ring_bytes<T, BN, ACT>();
   uint16_t* lut = reinterpret_cast<uint16_t*>(staging + kEpiWarps * kStagingTile);
   float* bias_f32 = reinterpret_cast<float*>(staging + kEpiWarps * kStagingTile + lut_bytes<T, ACT>());
-  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpiWarps * kStagingTile + lut_bytes<T, ACT>() + kBiasBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpiWarps * kStagingTile + lut_bytes<T, ACT>() + bias_bytes<ACT>());
   uint64_t* full = bars;                  // [kStages] TMA landed
   uint64_t* empty = bars + kStages;       // [kStages] MMA finished reading
   uint64_t* acc_full = bars + 2 * kStages;      // [2] accumulator complete
   uint64_t* acc_empty = bars + 2 * kStages + 2; // [2] accumulator drained by the epilogue
   uint64_t* res_bars = bars + 2 * kStages + 4;  // [kEpiWarps] residual tile landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bars + kEpiWarps);
+  uint64_t* quad_bars = res_bars + kEpiWarps;    // [2 sets][4] LayerNorm epilogue: row partial sums published
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(quad_bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -297,6 +300,7 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4 * kCG); }
     for (int w = 0; w < kEpiWarps; ++w) mbar_init(&res_bars[w], 1);
+    for (int q = 0; q < 8; ++q) mbar_init(&quad_bars[q], (uint32_t)((p.N + BN / kCG - 1) / (BN / kCG)));
     *abort_flag = 0;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -375,7 +379,7 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       if (blockIdx.x == 0) { g_lin_prof[2] = prof_acc[2]; g_lin_prof[3] = prof_acc[3]; g_lin_prof[4] = prof_acc[4]; }
 #endif
     }
-  } else if (warp - 2 < 4 * kCG) {
+  } else {
     // ---------------------------------------------------------------- epilogue
     // Each lane owns one accumulator row (that is how tensor memory is read).  It applies bias,
     // rounding, activation and residual and parks 16-byte pieces in a staging tile laid out with
@@ -384,7 +388,12 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     // (TMA load into the staging tile, consumed in place).  Two staging tiles per warp let the
     // store of one unit overlap the arithmetic of the next.
     const int quad = warp & 3;              // tensor-memory lanes [32*quad, 32*quad+32)
-    const int group = (warp - 2) >> 2;      // which column group of the tile
+    // A tile occupies 4 * kCG warps.  When that is only half of the epilogue warps (64-column
+    // tiles) the other half forms a second set that takes every other tile -- and with it the
+    // other accumulator -- so two epilogues are in flight and their latencies overlap.
+    constexpr int kSets = kEpiWarps / (4 * kCG);
+    const int set = ((warp - 2) >> 2) / kCG;
+    const int group = ((warp - 2) >> 2) % kCG;  // which column group of the tile
     constexpr int kColsPerWarp = BN / kCG;
     constexpr int UW = unit_cols<BN>();     // columns per staging unit (32 or 64)
     constexpr int RB = UW * 2;        // bytes per staged row (64 or 128) == swizzle span
@@ -392,28 +401,35 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     constexpr int RPW = 128 / RB;     // rows per 128-byte bank window
     unsigned char* buf = staging + (warp - 2) * kStagingTile;
     uint64_t* res_bar = &res_bars[warp - 2];
-    float* my_bias = bias_f32 + (warp - 2) * 64;
+    constexpr int kParamFloats = ACT == 2 ? 192 : 64;  // [0,64) bias; LayerNorm: [64,128) gamma, [128,192) beta
+    float* my_bias = bias_f32 + (warp - 2) * kParamFloats;
+    float* stats = bias_f32 + kEpiWarps * kParamFloats;  // LayerNorm: [2][kEpiWarps * 32] per-row partial sums
     const T* bias = static_cast<const T*>(p.bias);
     const bool has_res = p.residual != nullptr;
-    int acc = 0;
-    uint32_t acc_phase = 0, unit = 0;
+    uint32_t unit = 0, ln_phase = 0;
+    uint64_t* quad_bar = &quad_bars[set * 4 + quad];
+    const int stat_slot = ((set * 4 + quad) * kCG) * 32 + lane;  // + group * 32
     if (ACT == 1) {
       // Fill the GELU table (epilogue warps only; the pipeline fills meanwhile).
       // One erff serves both signs: erff is odd, so 1 + erff(-z) == 1 - erff(z) exactly.
-      for (uint32_t d = threadIdx.x - 64; d < GeluLut<T>::kSpan; d += 32 * 4 * kCG) {
+      for (uint32_t d = threadIdx.x - 64; d < GeluLut<T>::kSpan; d += 32 * kEpiWarps) {
         const float x = unpack2<T>(GeluLut<T>::kLo + d).x;
         const float e = erff(x * 0.70710678118654752440f);
         lut[d] = (uint16_t)(pack2<T>(0.5f * x * (1.0f + e), 0.f) & 0xFFFFu);
         lut[d + GeluLut<T>::kSpan] = (uint16_t)(pack2<T>(0.5f * -x * (1.0f - e), 0.f) & 0xFFFFu);
       }
-      asm volatile("bar.sync 1, %0;" ::"n"(32 * 4 * kCG) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
     }
     pdl_wait();  // residual may be the previous kernel's output; y may be read by it
 #ifdef DCNB200_LINEAR_PROFILE
     long long prof_acc[16] = {0};
 #endif
     PROF_T0();
-    for (long long t = blockIdx.x; t < n_tiles_total && !*abort_flag; t += gridDim.x) {
+    long long t = blockIdx.x;
+    for (uint32_t it = 0; t < n_tiles_total && !*abort_flag; t += gridDim.x, ++it) {
+      if (kSets > 1 && (int)(it % kSets) != set) continue;
+      const int acc = (int)(it & 1);
+      const uint32_t acc_phase = (it >> 1) & 1;
       const int mt = (int)(t / p.n_tiles), nt = (int)(t % p.n_tiles);
       PROF_ADD(5);
       if (!mbar_wait_bounded(&acc_full[acc], acc_phase)) {
@@ -423,6 +439,17 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       tc_fence_after();
       PROF_ADD(6);
       const int row0 = mt * kBM + quad * 32;
+      // The residual tile is needed the moment the accumulator is read; fetching it from DRAM
+      // only then would expose the full latency once per tile, so the next tile's residual is
+      // pulled into L2 now, a whole tile ahead.
+      if (has_res && lane == 0 && t + (long long)kSets * gridDim.x < n_tiles_total) {
+        const long long tn = t + (long long)kSets * gridDim.x;
+        const int mt_n = (int)(tn / p.n_tiles), nt_n = (int)(tn % p.n_tiles);
+        for (int c = 0; c < kColsPerWarp; c += UW) {
+          const int col_n = nt_n * BN + group * kColsPerWarp + c;
+          if (col_n < p.N) tma_prefetch_2d(&map_r, col_n, mt_n * kBM + quad * 32);
+        }
+      }
       const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + group * kColsPerWarp);
 #pragma unroll 1
       for (int c = 0; c < kColsPerWarp; c += UW, ++unit) {
@@ -440,6 +467,7 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         // flight while the warp stages this unit's bias as fp32 (two columns per lane, zero
         // where there is none) so that the per-row loop reads it with 16-byte shared loads.
         uint32_t v[32];
+        uint32_t yreg[ACT == 2 ? UW / 2 : 1];  // this lane's row of the result, kept for the LayerNorm pass
         tmem_ld_32x32(taddr0 + (uint32_t)c, v);
 #pragma unroll
         for (int q = lane * 2; q < UW; q += 64) {
@@ -447,6 +475,12 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
           float2 b = make_float2(0.f, 0.f);
           if (bias != nullptr && col < p.N) b = unpack2<T>(__ldg(reinterpret_cast<const uint32_t*>(bias + col)));
           *reinterpret_cast<float2*>(my_bias + q) = b;
+          if (ACT == 2) {
+            const T* gamma = static_cast<const T*>(p.gamma);
+            const T* beta = static_cast<const T*>(p.beta);
+            *reinterpret_cast<float2*>(my_bias + 64 + q) = unpack2<T>(__ldg(reinterpret_cast<const uint32_t*>(gamma + col)));
+            *reinterpret_cast<float2*>(my_bias + 128 + q) = unpack2<T>(__ldg(reinterpret_cast<const uint32_t*>(beta + col)));
+          }
         }
         __syncwarp();
         if (has_res && !mbar_wait_bounded(res_bar, unit & 1)) {
@@ -479,6 +513,10 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
               }
             }
             *slot = make_uint4(o[0], o[1], o[2], o[3]);
+            if (ACT == 2) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) yreg[((cc + j) >> 1) + q] = o[q];
+            }
           }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -489,11 +527,77 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
         PROF_ADD(9);
+        if (ACT == 2) {
+          // LayerNorm of the row just produced (second output z).  A row's columns are spread
+          // over the column-group warps of this quadrant; they exchange per-row partial sums
+          // through shared memory and meet at an mbarrier (one per quadrant, one arrival per
+          // warp that owns columns; bounded waits like everywhere else).  Each warp reduces its own
+          // columns to (mean, sum of squared deviations) and the pairs are combined exactly
+          // (Chan et al.), so one exchange per tile suffices and nothing cancels.
+          const int n_groups = (p.N + kColsPerWarp - 1) / kColsPerWarp;  // groups that own columns
+          // this warp's share of the row: mean and sum of squared deviations of its UW columns
+          float s1 = 0.f;
+#pragma unroll
+          for (int q = 0; q < UW / 2; ++q) { const float2 f = unpack2<T>(yreg[q]); s1 += f.x + f.y; }
+          const float m_loc = s1 * (1.f / (float)UW);
+          float s2 = 0.f;
+#pragma unroll
+          for (int q = 0; q < UW / 2; ++q) {
+            const float2 f = unpack2<T>(yreg[q]);
+            s2 = fmaf(f.x - m_loc, f.x - m_loc, s2);
+            s2 = fmaf(f.y - m_loc, f.y - m_loc, s2);
+          }
+          stats[stat_slot + group * 32] = m_loc;
+          stats[kEpiWarps * 32 + stat_slot + group * 32] = s2;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(quad_bar);
+          if (!mbar_wait_bounded(quad_bar, ln_phase) && lane == 0) { atomicExch(p.status, kStatusStageTimeout); *abort_flag = 1; }
+          ln_phase ^= 1;
+          // combine the groups' (mean, M2) pairs: M2 = sum M2_g + UW * sum (mean_g - mean)^2
+          float tot = 0.f;
+          for (int g2 = 0; g2 < n_groups; ++g2) tot += stats[stat_slot + g2 * 32];
+          const float mean = tot / (float)n_groups;
+          float m2 = 0.f;
+          for (int g2 = 0; g2 < n_groups; ++g2) {
+            const float dm = stats[stat_slot + g2 * 32] - mean;
+            m2 += stats[kEpiWarps * 32 + stat_slot + g2 * 32] + (float)UW * dm * dm;
+          }
+          const float rstd = rsqrtf(m2 / (float)p.N + p.eps);
+          // z is staged beside y when the tile leaves room (32-column units use half of the
+          // warp's staging tile); otherwise the store of y must first finish reading it
+          unsigned char* zbuf = buf + (UW == 32 ? kStagingTile / 2 : 0);
+          if (UW != 32) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+          }
+#pragma unroll
+          for (int j = 0; j < UW; j += 8) {
+            const float4 gA = *reinterpret_cast<const float4*>(my_bias + 64 + j);
+            const float4 gB = *reinterpret_cast<const float4*>(my_bias + 64 + j + 4);
+            const float4 tA = *reinterpret_cast<const float4*>(my_bias + 128 + j);
+            const float4 tB = *reinterpret_cast<const float4*>(my_bias + 128 + j + 4);
+            const float g8[8] = {gA.x, gA.y, gA.z, gA.w, gB.x, gB.y, gB.z, gB.w};
+            const float t8[8] = {tA.x, tA.y, tA.z, tA.w, tB.x, tB.y, tB.z, tB.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              const float2 f = unpack2<T>(yreg[(j + e) >> 1]);
+              o[e >> 1] = pack2<T>(fmaf((f.x - mean) * rstd, g8[e], t8[e]), fmaf((f.y - mean) * rstd, g8[e + 1], t8[e + 1]));
+            }
+            *reinterpret_cast<uint4*>(zbuf + lane * RB + (((j >> 3) ^ ((lane / RPW) % CPR)) << 4)) =
+                make_uint4(o[0], o[1], o[2], o[3]);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&map_z, zbuf, col0, row0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 #ifdef DCNB200_LINEAR_PROFILE
@@ -547,7 +651,7 @@ bool make_map(CUtensorMap* m, int dtype, const void* base, long long rows, int c
 
 struct LinearArgs {
   int dtype;
-  const void* x; const void* w; const void* residual; void* y;
+  const void* x; const void* w; const void* residual; void* y; void* z;
 };
 
 template <typename T, int BN, int ACT>
@@ -562,21 +666,27 @@ cudaError_t launch_act(const LinearArgs& a, LinearParams p, int sms, cudaStream_
                                          (int)smem_bytes<T, BN, ACT>());
   });
   if (attr_err[dev] != cudaSuccess) return attr_err[dev];
-  CUtensorMap mx, mw, my, mr;
+  CUtensorMap mx, mw, my, mr, mz;
   constexpr int UW = unit_cols<BN>();
   if (!make_map(&mx, a.dtype, a.x, p.M, p.K, kBM, kBK) || !make_map(&mw, a.dtype, a.w, p.N, p.K, BN, kBK) ||
       !make_map(&my, a.dtype, a.y, p.M, p.N, 32, UW) ||
-      !make_map(&mr, a.dtype, a.residual ? a.residual : a.y, p.M, p.N, 32, UW))
+      !make_map(&mr, a.dtype, a.residual ? a.residual : a.y, p.M, p.N, 32, UW) ||
+      !make_map(&mz, a.dtype, a.z ? a.z : a.y, p.M, p.N, 32, UW))
     return cudaErrorNotSupported;
   p.n_tiles = (p.N + BN - 1) / BN;
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   const int grid = (int)(tiles < sms ? tiles : sms);
   return launch_overlapped(linear_kernel<T, BN, ACT>, dim3((unsigned)grid), dim3(kGemmThreads),
-                           smem_bytes<T, BN, ACT>(), stream, mx, mw, my, mr, p);
+                           smem_bytes<T, BN, ACT>(), stream, mx, mw, my, mr, mz, p);
 }
 
 template <typename T>
 cudaError_t launch_bn(int bn, int act, const LinearArgs& a, const LinearParams& p, int sms, cudaStream_t stream) {
+  if (act == 2) {
+    if (bn == 256) return launch_act<T, 256, 2>(a, p, sms, stream);
+    if (bn == 128) return launch_act<T, 128, 2>(a, p, sms, stream);
+    return launch_act<T, 64, 2>(a, p, sms, stream);
+  }
   if (act == 1) {
     if (bn == 256) return launch_act<T, 256, 1>(a, p, sms, stream);
     if (bn == 128) return launch_act<T, 128, 1>(a, p, sms, stream);
@@ -590,9 +700,10 @@ cudaError_t launch_bn(int bn, int act, const LinearArgs& a, const LinearParams& 
 }  // namespace
 
 // dtype: 1 fp16, 2 bf16.  Returns cudaErrorNotSupported when the driver lacks tensor maps.
+// act 2 (LayerNorm as second output z; N <= 256) needs gamma, beta, eps and z.
 cudaError_t launch_linear_fwd(int dtype, const void* x, const void* w, const void* bias, const void* residual,
                               void* y, long long M, int N, int K, int act, int sms, int* status,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, const void* gamma, const void* beta, float eps, void* z) {
   // Tile width: the widest of 256/128/64 that N fills, unless a narrower one wastes less of the
   // last wave of CTAs (cost model: waves x (columns + fixed per-tile overhead)).
   const int m_tiles = (int)((M + kBM - 1) / kBM);
@@ -608,13 +719,15 @@ cudaError_t launch_linear_fwd(int dtype, const void* x, const void* w, const voi
     const double cost = (double)((tiles + sms - 1) / sms) * (cand + 48);
     if (cost < best * 0.98) { best = cost; bn = cand; }
   }
+  if (act == 2) bn = N > 128 ? 256 : (N > 64 ? 128 : 64);  // a row must lie in one tile
   LinearParams p;
   p.M = M; p.N = N; p.K = K;
   p.m_tiles = (int)((M + kBM - 1) / kBM);
   p.n_tiles = 0;
   p.k_blocks = (K + kBK - 1) / kBK;
   p.bias = bias; p.residual = residual; p.y = y; p.status = status;
-  const LinearArgs a{dtype, x, w, residual, y};
+  p.gamma = gamma; p.beta = beta; p.eps = eps;
+  const LinearArgs a{dtype, x, w, residual, y, z};
   if (dtype == 1) return launch_bn<__half>(bn, act, a, p, sms, stream);
   return launch_bn<__nv_bfloat16>(bn, act, a, p, sms, stream);
 }

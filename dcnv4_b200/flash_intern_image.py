@@ -131,6 +131,16 @@ class DownsampleLayer(nn.Module):
         return x.permute(0, 2, 3, 1).reshape(N, H * W, 2 * C), (H, W)
 
 
+def _single_layer_norm(module) -> Optional[nn.LayerNorm]:
+    """The nn.LayerNorm inside a channels-last norm layer built by build_norm_layer, if that is
+    all the layer consists of."""
+    if isinstance(module, nn.LayerNorm):
+        return module
+    if isinstance(module, nn.Sequential) and len(module) == 1 and isinstance(module[0], nn.LayerNorm):
+        return module[0]
+    return None
+
+
 class MLPLayer(nn.Module):
     def __init__(self, in_features, hidden_features=None, out_features=None, act_layer="GELU",
                  mlp_fc2_bias=False, drop=0.0):
@@ -142,14 +152,16 @@ class MLPLayer(nn.Module):
         self.fc2 = nn.Linear(hidden_features, out_features, bias=mlp_fc2_bias)
         self.drop = nn.Dropout(drop)
 
-    def forward(self, x, shape=None, residual=None):
-        """fc2(act(fc1(x))) [+ residual]; at inference GELU and the residual addition are fused
-        into the two matrix products (dropout is the identity there)."""
+    def forward(self, x, shape=None, residual=None, norm=None):
+        """fc2(act(fc1(x))) [+ residual], and with `norm` (an nn.LayerNorm) the pair
+        (result, norm(result)); at inference GELU, the residual addition and the LayerNorm are
+        fused into the two matrix products (dropout is the identity there)."""
         if isinstance(self.act, nn.GELU) and self.act.approximate == "none" and not (self.training and self.drop.p > 0):
             h = ops.linear_module_forward(x, self.fc1, None, "gelu")
-            return ops.linear_module_forward(h, self.fc2, residual)
+            return ops.linear_module_forward(h, self.fc2, residual, "none", norm)
         y = self.drop(self.fc2(self.drop(self.act(self.fc1(x)))))
-        return y if residual is None else residual + y
+        y = y if residual is None else residual + y
+        return y if norm is None else (y, norm(y))
 
 
 class InternImageLayer(nn.Module):
@@ -179,16 +191,45 @@ class InternImageLayer(nn.Module):
             x = x + self.drop_path(self.gamma1 * a if self.layer_scale else a)
             m = self.norm2(self.mlp(x, shape))
             x = x + self.drop_path(self.gamma2 * m if self.layer_scale else m)
-        elif not self.layer_scale and (not self.training or isinstance(self.drop_path, nn.Identity)):
-            # plain residual blocks: the additions ride on the output projection and on fc2
-            x = self.dcn(self.norm1(x), shape, residual=x)
-            x = self.mlp(self.norm2(x), shape, residual=x)
+        elif self._plain_residual():
+            x = self._chained(x, shape, None, None)[0]
         else:
             a = self.dcn(self.norm1(x), shape)
             x = x + self.drop_path(self.gamma1 * a if self.layer_scale else a)
             m = self.mlp(self.norm2(x), shape)
             x = x + self.drop_path(self.gamma2 * m if self.layer_scale else m)
         return x
+
+    def _plain_residual(self) -> bool:
+        """Pre-norm layer whose two branches are added as they are (no layer scale, no active
+        stochastic depth): the additions can ride on the output projection and on fc2."""
+        return (not self.post_norm and not self.layer_scale
+                and (not self.training or isinstance(self.drop_path, nn.Identity)))
+
+    def forward_chained(self, x, shape, normed=None, next_norm=None):
+        """The layer for callers that chain layers (InternImageBlock): `normed` is norm1(x) if the
+        previous layer already produced it, `next_norm` the LayerNorm that will be applied to
+        this layer's result.  Returns (result, next_norm(result) or None).  At inference each
+        LayerNorm is computed in the epilogue of the matrix product that precedes it."""
+        if not self._plain_residual() or (self.with_cp and x.requires_grad):
+            x = self.forward(x, shape)
+            return x, (None if next_norm is None else next_norm(x))
+        return self._chained(x, shape, normed, next_norm)
+
+    def _chained(self, x, shape, normed, next_norm):
+        n2 = _single_layer_norm(self.norm2)
+        a_in = normed if normed is not None else self.norm1(x)
+        if n2 is not None:
+            x, m_in = self.dcn(a_in, shape, residual=x, norm=n2)
+        else:
+            x = self.dcn(a_in, shape, residual=x)
+            m_in = self.norm2(x)
+        nn_ = _single_layer_norm(next_norm) if next_norm is not None else None
+        if nn_ is not None:
+            x, nxt = self.mlp(m_in, shape, residual=x, norm=nn_)
+            return x, nxt
+        x = self.mlp(m_in, shape, residual=x)
+        return x, (None if next_norm is None else next_norm(x))
 
     def forward(self, x, shape):
         if self.with_cp and x.requires_grad:
@@ -218,10 +259,12 @@ class InternImageBlock(nn.Module):
         self.downsample = DownsampleLayer(channels=channels, norm_layer=norm_layer) if downsample else None
 
     def forward(self, x, shape):
-        for blk in self.blocks:
-            x = blk(x, shape)
+        normed = None  # norm1 of the next layer (or the level's final norm) applied to x, if already known
+        for i, blk in enumerate(self.blocks):
+            nxt = self.blocks[i + 1].norm1 if i + 1 < len(self.blocks) else (None if self.post_norm else self.norm)
+            x, normed = blk.forward_chained(x, shape, normed, nxt)
         if not self.post_norm:
-            x = self.norm(x)
+            x = normed if normed is not None else self.norm(x)
         if self.downsample is not None:
             x, shape = self.downsample(x, shape)
         return x, shape

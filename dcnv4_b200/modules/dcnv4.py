@@ -74,11 +74,12 @@ class DCNv4(nn.Module):
             if self.output_proj.bias is not None:
                 constant_(self.output_proj.bias.data, 0.)
 
-    def forward(self, input, shape=None, residual=None):
+    def forward(self, input, shape=None, residual=None, norm=None):
         """input (N, L, C) with L = H*W; `shape` = (H, W) when the map is not square.
-        Returns (N, L, C).  `residual` (N, L, C), an extension over the reference signature,
-        is added to the result; at inference the addition is fused into the output
-        projection."""
+        Returns (N, L, C).  Two extensions over the reference signature serve the layer that
+        embeds this module: `residual` (N, L, C) is added to the result, and with `norm` (an
+        nn.LayerNorm over C) the pair `(result, norm(result))` is returned; at inference both are
+        fused into the output projection."""
         N, L, C = input.shape
         if shape is not None:
             H, W = shape
@@ -110,5 +111,6 @@ class DCNv4(nn.Module):
 
         x = x.view(N, L, -1)
         if not self.without_pointwise:
-            return ops.linear_module_forward(x, self.output_proj, residual)
-        return x if residual is None else residual + x
+            return ops.linear_module_forward(x, self.output_proj, residual, "none", norm)
+        x = x if residual is None else residual + x
+        return x if norm is None else (x, norm(x))

@@ -232,6 +232,38 @@ def linear_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
     return y
 
 
+def linear_layer_norm_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                              residual: Optional[torch.Tensor], ln_weight: torch.Tensor, ln_bias: torch.Tensor,
+                              eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(y, LayerNorm(y)) with y = x @ weight.T + bias [+ residual], one tensor-core kernel
+    (forward only; fp16 / bf16; out_features a multiple of 32, at most 256)."""
+    _check_tensor(x, "input")
+    _check_tensor(weight, "weight")
+    N, K = weight.shape
+    if x.shape[-1] != K or weight.dtype != x.dtype:
+        raise RuntimeError("weight must be (out_features, in_features) in the dtype of the input")
+    for t, name in ((bias, "bias"), (residual, "residual"), (ln_weight, "ln_weight"), (ln_bias, "ln_bias")):
+        if t is not None:
+            _check_tensor(t, name)
+            if t.dtype != x.dtype:
+                raise RuntimeError(f"{name} must have the dtype of the input")
+    M = x.numel() // max(K, 1)
+    if (bias is not None and bias.numel() != N) or ln_weight.numel() != N or ln_bias.numel() != N:
+        raise RuntimeError("bias and LayerNorm parameters must have out_features elements")
+    if residual is not None and residual.numel() != M * N:
+        raise RuntimeError("residual must have the shape of the output")
+    y = torch.empty(x.shape[:-1] + (N,), dtype=x.dtype, device=x.device)
+    z = torch.empty_like(y)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().dcnv4b200_linear_ln_fwd(x.data_ptr(), weight.data_ptr(),
+                                                bias.data_ptr() if bias is not None else None,
+                                                residual.data_ptr() if residual is not None else None,
+                                                y.data_ptr(), ln_weight.data_ptr(), ln_bias.data_ptr(), float(eps),
+                                                z.data_ptr(), _code(x), M, N, K, _stream(x))
+    _lib.check(rc, "linear_layer_norm_forward")
+    return y, z
+
+
 def linear_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """True when `linear_forward` covers this input (dtype, size, layout)."""
     if not (x.is_cuda and x.is_contiguous() and x.dtype in (torch.float16, torch.bfloat16) and x.numel() > 0):
@@ -250,21 +282,35 @@ FUSED_LINEAR_MAX_K = 1024
 
 
 def linear_module_forward(x: torch.Tensor, lin: "torch.nn.Linear", residual: Optional[torch.Tensor] = None,
-                          activation: str = "none") -> torch.Tensor:
-    """`residual + act(lin(x))` for an nn.Linear: one fused tensor-core kernel when autograd
-    is not needed and the kernel covers the input, else the stock PyTorch operations (same
-    result up to fp rounding: the fused kernel rounds at the same points)."""
+                          activation: str = "none", norm: Optional["torch.nn.LayerNorm"] = None):
+    """`y = residual + act(lin(x))` for an nn.Linear, and with `norm` (an nn.LayerNorm over the
+    output features) the pair `(y, norm(y))`.  One fused tensor-core kernel when autograd is not
+    needed and the kernel covers the input, else the stock PyTorch operations (same result up
+    to fp rounding: the fused kernel rounds at the same points)."""
     needs_grad = torch.is_grad_enabled() and (x.requires_grad or lin.weight.requires_grad)
-    if (FUSED_LINEAR and not needs_grad and not torch.is_autocast_enabled() and linear_supported(x, lin.weight)
-            and lin.in_features <= FUSED_LINEAR_MAX_K
-            and (lin.bias is None or (lin.bias.dtype == x.dtype and lin.bias.data_ptr() % 16 == 0))
-            and (residual is None or (residual.dtype == x.dtype and residual.is_contiguous()
-                                      and residual.data_ptr() % 16 == 0))):
-        return linear_forward(x, lin.weight, lin.bias, residual, activation)
-    y = torch.nn.functional.linear(x, lin.weight, lin.bias)
-    if activation == "gelu":
-        y = torch.nn.functional.gelu(y)
-    return y if residual is None else residual + y
+    fused = (FUSED_LINEAR and not needs_grad and not torch.is_autocast_enabled() and linear_supported(x, lin.weight)
+             and lin.in_features <= FUSED_LINEAR_MAX_K
+             and (lin.bias is None or (lin.bias.dtype == x.dtype and lin.bias.data_ptr() % 16 == 0))
+             and (residual is None or (residual.dtype == x.dtype and residual.is_contiguous()
+                                       and residual.data_ptr() % 16 == 0)))
+    if fused and norm is not None and activation == "none" and _norm_fusable(norm, lin.out_features, x.dtype):
+        return linear_layer_norm_forward(x, lin.weight, lin.bias, residual, norm.weight, norm.bias, norm.eps)
+    if fused:
+        y = linear_forward(x, lin.weight, lin.bias, residual, activation)
+    else:
+        y = torch.nn.functional.linear(x, lin.weight, lin.bias)
+        if activation == "gelu":
+            y = torch.nn.functional.gelu(y)
+        if residual is not None:
+            y = residual + y
+    return y if norm is None else (y, norm(y))
+
+
+def _norm_fusable(norm, features: int, dtype: torch.dtype) -> bool:
+    return (isinstance(norm, torch.nn.LayerNorm) and norm.elementwise_affine and norm.bias is not None
+            and tuple(norm.normalized_shape) == (features,) and features % 32 == 0 and features <= 256
+            and norm.weight.dtype == dtype and norm.bias.dtype == dtype
+            and norm.weight.data_ptr() % 16 == 0 and norm.bias.data_ptr() % 16 == 0)
 
 
 def dcnv4_corners(p_offset, H, W, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, dilation_h,

@@ -177,6 +177,21 @@ int dcnv4b200_linear_fwd(const void* x, const void* weight, const void* bias, co
                          int dtype, long long M, int N, int K, int activation, void* stream);
 
 /*
+ * dcnv4b200_linear_fwd (no activation) that also returns the LayerNorm of its result:
+ *     y = x . weight^T + bias [+ residual]               as above, rounded to `dtype`
+ *     z = LayerNorm(y) * gamma + beta                    over the N columns of each row, fp32 statistics
+ * In a pre-norm FlashInternImage layer every residual sum is followed by a LayerNorm
+ * (classification/models/flash_intern_image.py:424-425: x + dcn(norm1(x)), x + mlp(norm2(x))),
+ * which the reference runs as a separate torch.nn.LayerNorm kernel.  Here the row is
+ * normalised while it is still on chip.
+ *   gamma, beta (N) in `dtype`; y and z (M,N).  N must be a multiple of 32 and at most 256
+ *   (a row has to lie inside one tile; DCNV4B200_ERR_UNSUPPORTED / _ERR_CHANNELS otherwise).
+ */
+int dcnv4b200_linear_ln_fwd(const void* x, const void* weight, const void* bias, const void* residual, void* y,
+                            const void* gamma, const void* beta, float eps, void* z, int dtype, long long M,
+                            int N, int K, void* stream);
+
+/*
  * Read and clear the current device's kernel status word (0 = no kernel ever gave up on a
  * bounded wait for its staged tile).  Synchronises the device; meant for tests and
  * post-mortems, not for the hot path.  No counterpart in the reference.

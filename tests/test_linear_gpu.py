@@ -92,6 +92,51 @@ def test_output_may_alias_residual_and_batch_dims_are_kept():
     torch.testing.assert_close(r.float(), want, **TOL[torch.float16])
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (1, 32, 8), (3136, 64, 256), (1000, 128, 128), (777, 128, 512),
+                                   (196, 256, 256), (4099, 256, 1024), (5000, 96, 64), (333, 192, 72)])
+def test_linear_with_layernorm_epilogue(M, N, K, dtype):
+    """(y, LayerNorm(y)) from one kernel: y must equal the plain fused kernel's bit for bit, and z
+    the LayerNorm of that y (fp32 statistics) within one unit in the last place."""
+    from dcnv4_b200 import ops
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV).to(dtype)
+    w = (torch.randn(N, K, device=DEV) / K ** 0.5).to(dtype)
+    b = torch.randn(N, device=DEV).to(dtype)
+    r = (torch.randn(M, N, device=DEV) * 2 + 1).to(dtype)
+    g = (torch.randn(N, device=DEV) * 0.5 + 1).to(dtype)
+    beta = torch.randn(N, device=DEV).to(dtype)
+    for bias, res in [(b, r), (None, None), (b, None)]:
+        y, z = ops.linear_layer_norm_forward(x, w, bias, res, g, beta, 1e-6)
+        assert torch.equal(y, ops.linear_forward(x, w, bias, res))
+        ref = F.layer_norm(y.float(), (N,), g.float(), beta.float(), 1e-6)
+        torch.testing.assert_close(z.float(), ref, **TOL[dtype])
+    assert ops.device_status() == 0
+
+
+def test_layernorm_epilogue_limits_and_module_helper():
+    from dcnv4_b200 import _lib, ops
+    lib = _lib.lib()
+    x = torch.randn(16, 64, device=DEV, dtype=torch.float16)
+    st = torch.cuda.current_stream().cuda_stream
+    for n, want in ((512, -6), (40, -8)):         # a row must fit one tile; columns in units of 32
+        w = torch.randn(n, 64, device=DEV, dtype=torch.float16)
+        y = torch.empty(16, n, device=DEV, dtype=torch.float16)
+        g = torch.ones(n, device=DEV, dtype=torch.float16)
+        assert lib.dcnv4b200_linear_ln_fwd(x.data_ptr(), w.data_ptr(), None, None, y.data_ptr(), g.data_ptr(),
+                                           g.data_ptr(), 1e-6, y.data_ptr(), 1, 16, n, 64, st) == want
+    # the module helper falls back to separate kernels where the fused one does not apply
+    lin = torch.nn.Linear(64, 512).to(DEV).half()
+    norm = torch.nn.LayerNorm(512, eps=1e-6).to(DEV).half()
+    with torch.no_grad():
+        y, z = ops.linear_module_forward(x, lin, None, "none", norm)
+        torch.testing.assert_close(z, norm(y), **TOL[torch.float16])
+        lin2 = torch.nn.Linear(64, 128).to(DEV).half()
+        norm2 = torch.nn.LayerNorm(128, eps=1e-6).to(DEV).half()
+        y2, z2 = ops.linear_module_forward(x, lin2, None, "none", norm2)      # fused
+        torch.testing.assert_close(z2, norm2(y2), **TOL[torch.float16])
+
+
 def test_linear_rejects_what_it_cannot_do():
     from dcnv4_b200 import _lib, ops
     lib = _lib.lib()

@@ -37,6 +37,9 @@ def test_every_dcn_layer_of_a_tiny_model_matches_the_oracle():
     for mod, args, kwargs, out in seen:
         inp = args[0]
         H, W = kwargs.get("shape") or args[1]
+        normed = None
+        if kwargs.get("norm") is not None:           # the layer asked for (result, norm(result))
+            out, normed = out
         N, L, C = inp.shape
         with torch.no_grad():
             v = mod.value_proj(inp).reshape(N, H, W, C)
@@ -47,6 +50,8 @@ def test_every_dcn_layer_of_a_tiny_model_matches_the_oracle():
             if kwargs.get("residual") is not None:      # the block lets the module add its skip path
                 ref = kwargs["residual"] + ref
         torch.testing.assert_close(out, ref, rtol=1e-3, atol=1e-4)
+        if normed is not None:
+            torch.testing.assert_close(normed, kwargs["norm"](out), rtol=1e-4, atol=1e-5)
 
 
 def test_flash_intern_image_t_fp16_inference_and_train_step():
