@@ -365,8 +365,8 @@ def _note(msg):
 
 
 def time_model_with_reference_kernels(torch, model, images, iters=5):
-    """ms per forward of `model` with the reference CUDA extension as the DCNv4 core, stock LayerNorm
-    and no CUDA graph; None when the extension is not built."""
+    """ms per forward of `model` with the reference CUDA extension as the DCNv4 core, stock LayerNorm,
+    nn.Linear / nn.GELU / separate additions and no CUDA graph; None when the extension is not built."""
     try:
         from oracle import ref_cuda
         if not ref_cuda.available():
@@ -375,6 +375,7 @@ def time_model_with_reference_kernels(torch, model, images, iters=5):
     except Exception:
         return None
     from dcnv4_b200 import flash_intern_image as fii
+    from dcnv4_b200 import ops as our_ops
     from dcnv4_b200.modules import dcnv4 as dcn_mod
 
     class RefCore:
@@ -382,8 +383,8 @@ def time_model_with_reference_kernels(torch, model, images, iters=5):
         def apply(x, om, kh, kw, sh, sw, ph, pw, dh, dw, G, Dg, scale, step, rc):
             return ref_cuda.dcnv4_forward(x, om, kh, kw, sh, sw, ph, pw, dh, dw, G, Dg, scale, rc, step)
 
-    saved_fn, saved_flag = dcn_mod.DCNv4Function, fii.LayerNorm.use_library_kernel
-    dcn_mod.DCNv4Function, fii.LayerNorm.use_library_kernel = RefCore, False
+    saved_fn, saved_flag, saved_fused = dcn_mod.DCNv4Function, fii.LayerNorm.use_library_kernel, our_ops.FUSED_LINEAR
+    dcn_mod.DCNv4Function, fii.LayerNorm.use_library_kernel, our_ops.FUSED_LINEAR = RefCore, False, False
     try:
         with torch.no_grad():
             for _ in range(2):
@@ -400,7 +401,7 @@ def time_model_with_reference_kernels(torch, model, images, iters=5):
         _note(f"reference-stack model leg failed: {type(exc).__name__}: {exc}")
         return None
     finally:
-        dcn_mod.DCNv4Function, fii.LayerNorm.use_library_kernel = saved_fn, saved_flag
+        dcn_mod.DCNv4Function, fii.LayerNorm.use_library_kernel, our_ops.FUSED_LINEAR = saved_fn, saved_flag, saved_fused
 
 
 def run_ours(args):
@@ -528,26 +529,34 @@ def run_ours(args):
     # ---- the caller of the hot path: FlashInternImage-T inference, random-init weights, fp16,
     #      batch sharded over the ranks (global batch 256), no collective
     model_ms, model_batch = float("nan"), max(1, MODEL_GLOBAL_BATCH // world)
+    model_weak_ms = float("nan")    # N > 1 only: the same forward with the full batch on every GPU
     model_ref_ms = None
     if not args.no_model and not args.case:
         import copy
         from dcnv4_b200.flash_intern_image import GraphedInference, flash_intern_image, fold_batchnorm_
         torch.manual_seed(0)
         model = flash_intern_image("t").to(dev).half().eval()
-        images = torch.randn(model_batch, 3, 224, 224, device=dev, dtype=torch.float16)
-        # inference form: BatchNorms folded into their convolutions, one CUDA graph per forward
-        graphed = GraphedInference(fold_batchnorm_(copy.deepcopy(model)), images)
-        for _ in range(3):
-            graphed(images)
-        barrier()
-        m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        m0.record()
-        for _ in range(MODEL_ITERS):
-            graphed(images)
-        m1.record()
-        barrier()
-        model_ms = m0.elapsed_time(m1) / MODEL_ITERS
-        del graphed
+        folded = fold_batchnorm_(copy.deepcopy(model))
+
+        def time_graphed(batch):
+            # inference form: BatchNorms folded into their convolutions, one CUDA graph per forward
+            imgs = torch.randn(batch, 3, 224, 224, device=dev, dtype=torch.float16)
+            graphed = GraphedInference(folded, imgs)
+            for _ in range(3):
+                graphed(imgs)
+            barrier()
+            m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            m0.record()
+            for _ in range(MODEL_ITERS):
+                graphed(imgs)
+            m1.record()
+            barrier()
+            return m0.elapsed_time(m1) / MODEL_ITERS, imgs
+
+        model_ms, images = time_graphed(model_batch)
+        if world > 1:
+            model_weak_ms, _ = time_graphed(MODEL_GLOBAL_BATCH)
+        del folded
         # the same network the way the reference stack executes it: eager launches, torch.nn.LayerNorm,
         # and the reference's own CUDA operator (oracle/_ref) in place of ours.  Baseline leg, rank 0 only.
         if rank == 0 and world == 1 and not args.no_ref_cuda:
@@ -565,10 +574,10 @@ def run_ours(args):
         sampler.stop()
 
     _note("all legs done, reducing times over ranks")
-    times = torch.tensor([elapsed_ms, e2e_ms, model_ms], dtype=torch.float64, device=dev)
+    times = torch.tensor([elapsed_ms, e2e_ms, model_ms, model_weak_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, model_ms = times.tolist()
+    elapsed_ms, e2e_ms, model_ms, model_weak_ms = times.tolist()
 
     if rank == 0:
         per_op = []
@@ -609,11 +618,14 @@ def run_ours(args):
                 "img_per_s": model_batch * world / model_ms * 1e3, "ms_per_batch": model_ms,
                 "batch_per_gpu": model_batch, "global_batch": model_batch * world, "dtype": "fp16",
                 "input": "224x224 synthetic", "weights": "random init", "parallelism": f"batch-sharded x{world}",
-                "execution": "BatchNorm folded into the convolutions, CUDA graph replay per forward, input copied "
-                             "into the graph's buffer each iteration",
+                "img_per_s_with_full_batch_per_gpu": None if model_weak_ms != model_weak_ms else
+                MODEL_GLOBAL_BATCH * world / model_weak_ms * 1e3,
+                "execution": "BatchNorm folded into the convolutions, tensor-core Linear with fused GELU / "
+                             "residual / LayerNorm, CUDA graph replay per forward, input copied into the graph's "
+                             "buffer each iteration",
                 "reference_stack_img_per_s": (model_batch / model_ref_ms * 1e3) if model_ref_ms else None,
-                "reference_stack": "same network, eager launches, torch.nn.LayerNorm, reference CUDA operator "
-                                   "(its forward is wrong at the 14x14 and 7x7 stages; timing only)"},
+                "reference_stack": "same network, eager launches, torch.nn.LayerNorm / Linear / GELU, reference "
+                                   "CUDA operator (its forward is wrong at the 14x14 and 7x7 stages; timing only)"},
         }
         if args.case or args.no_e2e:
             line["e2e"] = None
