@@ -420,8 +420,9 @@ int dcnv4b200_linear_ln_fwd(const void* x, const void* weight, const void* bias,
   if (!x || !weight || !y || !gamma || !beta || !z) return DCNV4B200_ERR_NULL;
   if (dtype != DCNV4B200_F16 && dtype != DCNV4B200_BF16) return DCNV4B200_ERR_DTYPE;
   if (M < 0 || N <= 0 || K <= 0) return DCNV4B200_ERR_SHAPE;
-  if (N % 32 != 0 || K % 8 != 0) return DCNV4B200_ERR_CHANNELS;
   if (N > 256) return DCNV4B200_ERR_UNSUPPORTED;  // a row has to fit one tile of the kernel
+  // every epilogue warp must own a full unit of columns: 32 up to N = 128, 64 above
+  if (N % (N > 128 ? 64 : 32) != 0 || K % 8 != 0) return DCNV4B200_ERR_CHANNELS;
   if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || !aligned16(z) || !aligned16(bias) ||
       !aligned16(residual) || !aligned16(gamma) || !aligned16(beta))
     return DCNV4B200_ERR_ALIGN;

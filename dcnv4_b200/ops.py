@@ -236,7 +236,7 @@ def linear_layer_norm_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optio
                               residual: Optional[torch.Tensor], ln_weight: torch.Tensor, ln_bias: torch.Tensor,
                               eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
     """(y, LayerNorm(y)) with y = x @ weight.T + bias [+ residual], one tensor-core kernel
-    (forward only; fp16 / bf16; out_features a multiple of 32, at most 256)."""
+    (forward only; fp16 / bf16; out_features at most 256 and a multiple of 32, of 64 above 128)."""
     _check_tensor(x, "input")
     _check_tensor(weight, "weight")
     N, K = weight.shape
@@ -323,7 +323,8 @@ def _sm_count(device) -> int:
 
 def _norm_fusable(norm, features: int, dtype: torch.dtype) -> bool:
     return (isinstance(norm, torch.nn.LayerNorm) and norm.elementwise_affine and norm.bias is not None
-            and tuple(norm.normalized_shape) == (features,) and features % 32 == 0 and features <= 256
+            and tuple(norm.normalized_shape) == (features,) and features <= 256
+            and features % (64 if features > 128 else 32) == 0
             and norm.weight.dtype == dtype and norm.bias.dtype == dtype
             and norm.weight.data_ptr() % 16 == 0 and norm.bias.data_ptr() % 16 == 0)
 

@@ -184,8 +184,9 @@ int dcnv4b200_linear_fwd(const void* x, const void* weight, const void* bias, co
  * (classification/models/flash_intern_image.py:424-425: x + dcn(norm1(x)), x + mlp(norm2(x))),
  * which the reference runs as a separate torch.nn.LayerNorm kernel.  Here the row is
  * normalised while it is still on chip.
- *   gamma, beta (N) in `dtype`; y and z (M,N).  N must be a multiple of 32 and at most 256
- *   (a row has to lie inside one tile; DCNV4B200_ERR_UNSUPPORTED / _ERR_CHANNELS otherwise).
+ *   gamma, beta (N) in `dtype`; y and z (M,N).  N must be at most 256 (a row has to lie inside
+ *   one tile) and a multiple of 32, of 64 above 128 (DCNV4B200_ERR_UNSUPPORTED / _ERR_CHANNELS
+ *   otherwise).
  */
 int dcnv4b200_linear_ln_fwd(const void* x, const void* weight, const void* bias, const void* residual, void* y,
                             const void* gamma, const void* beta, float eps, void* z, int dtype, long long M,

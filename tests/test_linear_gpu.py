@@ -119,7 +119,7 @@ def test_layernorm_epilogue_limits_and_module_helper():
     lib = _lib.lib()
     x = torch.randn(16, 64, device=DEV, dtype=torch.float16)
     st = torch.cuda.current_stream().cuda_stream
-    for n, want in ((512, -6), (40, -8)):         # a row must fit one tile; columns in units of 32
+    for n, want in ((512, -6), (40, -8), (160, -8)):   # a row must fit one tile; columns in units of 32 / 64
         w = torch.randn(n, 64, device=DEV, dtype=torch.float16)
         y = torch.empty(16, n, device=DEV, dtype=torch.float16)
         g = torch.ones(n, device=DEV, dtype=torch.float16)
