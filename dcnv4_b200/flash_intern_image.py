@@ -377,7 +377,10 @@ class GraphedInference:
         if not example.is_cuda:
             raise RuntimeError("GraphedInference needs a CUDA example input")
         self.model = model.eval()
-        self.static_in = example.clone()
+        # image batches are kept channels-last, the layout the stem wants: the copy into the static
+        # buffer then does the layout change and the stem's own conversion disappears from the graph
+        self.static_in = (example.clone(memory_format=torch.channels_last) if example.dim() == 4
+                          else example.clone())
         side = torch.cuda.Stream(device=example.device)
         side.wait_stream(torch.cuda.current_stream(example.device))
         with torch.cuda.stream(side), torch.no_grad():

@@ -46,3 +46,60 @@ def test_stem_and_downsample_shapes_on_cpu():
     down = DownsampleLayer(64).eval()
     z, shape = down(y.view(2, 16 * 12, 64), (16, 12))
     assert shape == (8, 6) and z.shape == (2, 48, 128)
+
+
+def test_fused_linear_predicates_reject_cpu_and_odd_inputs():
+    """The helpers that decide whether the fused tensor-core kernels apply: never on CPU tensors,
+    never for shapes the kernels do not cover -- the stock PyTorch path then runs and gives the
+    same interface (a tensor, or a (y, norm(y)) pair)."""
+    import torch
+    from dcnv4_b200 import ops
+    lin = torch.nn.Linear(64, 128)
+    norm = torch.nn.LayerNorm(128, eps=1e-6)
+    x = torch.randn(5, 7, 64)
+    assert not ops.linear_supported(x, lin.weight)
+    assert ops._norm_fusable(norm, 128, torch.float32)          # shape rule only; dtype / device gate elsewhere
+    assert not ops._norm_fusable(norm, 128, torch.float16)      # parameters must match the activations' dtype
+    assert not ops._norm_fusable(torch.nn.LayerNorm(160), 160, torch.float32)     # above 128: multiples of 64
+    assert not ops._norm_fusable(torch.nn.LayerNorm(512), 512, torch.float32)     # a row must fit one tile
+    assert not ops._norm_fusable(torch.nn.LayerNorm(128, elementwise_affine=False), 128, torch.float32)
+    with torch.no_grad():
+        y = ops.linear_module_forward(x, lin)
+        torch.testing.assert_close(y, lin(x))
+        r = torch.randn(5, 7, 128)
+        y2, z2 = ops.linear_module_forward(x, lin, r, "gelu", norm)
+        want = r + torch.nn.functional.gelu(lin(x))
+        torch.testing.assert_close(y2, want)
+        torch.testing.assert_close(z2, norm(want))
+
+
+def test_layers_chain_their_layernorms_without_changing_the_result():
+    """InternImageBlock hands each layer the already-normalised input and the next LayerNorm;
+    on CPU everything falls back to the stock modules, so the chained forward must equal the
+    plain layer-by-layer formula exactly."""
+    import torch
+    from dcnv4_b200 import flash_intern_image as fii
+    torch.manual_seed(0)
+    layer_cls = fii.InternImageLayer
+
+    class Core(torch.nn.Module):      # stands in for DCNv4 (CUDA only): same call signature
+        def __init__(self, channels, **kw):
+            super().__init__()
+            self.proj = torch.nn.Linear(channels, channels)
+
+        def forward(self, x, shape=None, residual=None, norm=None):
+            y = self.proj(x)
+            y = y if residual is None else residual + y
+            return y if norm is None else (y, norm(y))
+
+    blk = fii.InternImageBlock(core_op=Core, channels=32, depth=3, groups=2, downsample=False, drop_path=0.0).eval()
+    x = torch.randn(2, 16, 32)
+    with torch.no_grad():
+        got, _ = blk(x, (4, 4))
+        want = x
+        for layer in blk.blocks:
+            want = want + layer.dcn(layer.norm1(want), (4, 4))
+            want = want + layer.mlp(layer.norm2(want), (4, 4))
+        want = blk.norm(want)
+    torch.testing.assert_close(got, want)
+    assert isinstance(blk.blocks[0], layer_cls)
