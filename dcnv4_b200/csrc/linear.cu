@@ -21,7 +21,10 @@
 //                         to the storage type, GELU by table, residual; the result goes to a
 //                         swizzled staging tile and leaves through a TMA store, which writes
 //                         whole lines and clips the ragged edge of the matrix.  The residual
-//                         tile arrives by TMA load into the same staging tile.
+//                         tile arrives by TMA load into the same staging tile.  Optionally the
+//                         LayerNorm of the finished row leaves as a second output (ACT == 2).
+//                         64-column tiles need only eight of these warps; the other eight then
+//                         form a second set working on the other accumulator.
 // The double-buffered accumulator lets the epilogue of tile i overlap the products of tile
 // i+1.  Every mbarrier wait is bounded; a wait that runs out records kStatusStageTimeout in
 // the device status word, the roles leave their loops and the CTA frees its tensor memory.
