@@ -31,7 +31,7 @@ namespace dcnb200 {
 #define DCNB200_FWD_MINB 2
 #endif
 #ifndef DCNB200_BWD_MINB
-#define DCNB200_BWD_MINB 2
+#define DCNB200_BWD_MINB 3
 #endif
 
 constexpr int kThreads = 256;             // threads per CTA of the four main kernels
