@@ -190,3 +190,25 @@ def test_flash_intern_image_logits_do_not_depend_on_the_fused_path():
         finally:
             ops.FUSED_LINEAR = True
     torch.testing.assert_close(fused.float(), stock.float(), rtol=1e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("size", ["s", "l"])
+def test_post_norm_layer_scale_models_agree_with_the_stock_path(size):
+    """FlashInternImage-S / -L: post-norm, layer scale, depthwise offset convolution, channel counts
+    (80..640, 160..1280) that are not multiples of 64.  Only fc1+GELU and the plain projections
+    are fused there; the logits must not depend on it beyond fp16 rounding."""
+    from dcnv4_b200 import ops
+    from dcnv4_b200.flash_intern_image import flash_intern_image
+    torch.manual_seed(1)
+    model = flash_intern_image(size, depths=(1, 1, 2, 1)).to(DEV).half().eval()
+    x = torch.randn(2, 3, 96, 128, device=DEV, dtype=torch.float16)
+    with torch.no_grad():
+        fused = model(x)
+        ops.FUSED_LINEAR = False
+        try:
+            stock = model(x)
+        finally:
+            ops.FUSED_LINEAR = True
+    assert torch.isfinite(fused).all()
+    torch.testing.assert_close(fused.float(), stock.float(), rtol=1e-2, atol=2e-3)
+    assert ops.device_status() == 0
