@@ -435,6 +435,21 @@ int dcnv4b200_linear_ln_fwd(const void* x, const void* weight, const void* bias,
                                 static_cast<cudaStream_t>(stream), gamma, beta, eps, z);
 }
 
+int dcnv4b200_bias_act_fwd(const void* x, const void* bias, void* y, int dtype, long long rows, int C,
+                           int activation, void* stream) {
+  if (!x || !bias || !y) return DCNV4B200_ERR_NULL;
+  if (dtype != DCNV4B200_F16 && dtype != DCNV4B200_BF16) return DCNV4B200_ERR_DTYPE;
+  if (rows < 0 || C <= 0) return DCNV4B200_ERR_SHAPE;
+  if (activation != DCNV4B200_ACT_NONE && activation != DCNV4B200_ACT_GELU) return DCNV4B200_ERR_UNSUPPORTED;
+  if (C % 8 != 0) return DCNV4B200_ERR_CHANNELS;
+  if (!aligned16(x) || !aligned16(y) || !aligned16(bias)) return DCNV4B200_ERR_ALIGN;
+  if (rows == 0) return 0;
+  int* status = nullptr;
+  int sms = 1;
+  if (int rc = status_ptr(&status, &sms)) return rc;
+  return (int)launch_bias_act_fwd(dtype, x, bias, y, rows, C, activation, sms, static_cast<cudaStream_t>(stream));
+}
+
 int dcnv4b200_device_status(int* status_out) {
   if (!status_out) return DCNV4B200_ERR_NULL;
   int* status = nullptr;

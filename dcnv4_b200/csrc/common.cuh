@@ -447,6 +447,10 @@ cudaError_t launch_linear_fwd(int dtype, const void* x, const void* w, const voi
                               cudaStream_t stream, const void* gamma = nullptr, const void* beta = nullptr,
                               float eps = 0.f, void* z = nullptr);
 
+// y = act(x + bias) over the channels of a channels-last 16-bit tensor (bias_act.cu).
+cudaError_t launch_bias_act_fwd(int dtype, const void* x, const void* bias, void* y, long long rows, int C, int act,
+                                int sms, cudaStream_t s);
+
 size_t dcnv4_fwd_smem(const DcnParams& p, int elem);
 size_t dcnv4_bwd_smem(const DcnParams& p, int elem);
 size_t fda_fwd_smem(const FdaParams& p, int elem);

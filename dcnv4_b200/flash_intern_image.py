@@ -110,6 +110,12 @@ class StemLayer(nn.Module):
 
     def forward(self, x):
         x = x.contiguous(memory_format=torch.channels_last)
+        if (isinstance(self.norm1[0], nn.Identity) and isinstance(self.norm2[0], nn.Identity)
+                and isinstance(self.act, nn.GELU) and self.act.approximate == "none"):
+            # BatchNorms folded (fold_batchnorm_): their shift is the convolution bias, applied
+            # together with the GELU by one pass over the convolution's output
+            x = ops.conv2d_bias_act(x, self.conv1, "gelu")
+            return self.norm2(ops.conv2d_bias_act(x, self.conv2, "none")).contiguous()
         x = self.act(self.norm1(self.conv1(x)))
         return self.norm2(self.conv2(x)).contiguous()
 

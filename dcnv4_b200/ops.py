@@ -329,6 +329,45 @@ def _norm_fusable(norm, features: int, dtype: torch.dtype) -> bool:
             and norm.weight.data_ptr() % 16 == 0 and norm.bias.data_ptr() % 16 == 0)
 
 
+def bias_act_(x: torch.Tensor, bias: torch.Tensor, activation: str = "none") -> torch.Tensor:
+    """In place: x = act(x + bias) over the last dimension of a contiguous fp16 / bf16 CUDA
+    tensor (forward only).  `activation` is "none" or "gelu" (erf form)."""
+    _check_tensor(x, "input")
+    _check_tensor(bias, "bias")
+    if activation not in ("none", "gelu"):
+        raise ValueError("activation must be 'none' or 'gelu'")
+    C = x.shape[-1]
+    if bias.numel() != C or bias.dtype != x.dtype:
+        raise RuntimeError("bias must have the size of the last dimension and the dtype of the input")
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().dcnv4b200_bias_act_fwd(x.data_ptr(), bias.data_ptr(), x.data_ptr(), _code(x),
+                                               x.numel() // max(C, 1), C, 1 if activation == "gelu" else 0,
+                                               _stream(x))
+    _lib.check(rc, "bias_act_")
+    return x
+
+
+def conv2d_bias_act(x: torch.Tensor, conv: "torch.nn.Conv2d", activation: str = "none") -> torch.Tensor:
+    """act(conv(x)) for a biased nn.Conv2d on a channels-last image batch: at inference in fp16 /
+    bf16 the bias and the activation are applied in place by one pass over the convolution's
+    output instead of PyTorch's separate broadcast addition and activation kernels."""
+    F = torch.nn.functional
+    needs_grad = torch.is_grad_enabled() and (x.requires_grad or conv.weight.requires_grad)
+    if (FUSED_LINEAR and not needs_grad and not torch.is_autocast_enabled() and x.is_cuda and conv.bias is not None
+            and x.dtype in (torch.float16, torch.bfloat16) and conv.weight.dtype == x.dtype
+            and conv.bias.dtype == x.dtype and conv.out_channels % 8 == 0 and conv.padding_mode == "zeros"
+            and conv.bias.data_ptr() % 16 == 0):
+        y = F.conv2d(x, conv.weight, None, conv.stride, conv.padding, conv.dilation, conv.groups)
+        rows = y.permute(0, 2, 3, 1)            # channels-last storage seen as (N, H, W, C)
+        if rows.is_contiguous() and y.data_ptr() % 16 == 0:
+            bias_act_(rows, conv.bias, activation)
+            return y
+        y = y + conv.bias.view(1, -1, 1, 1)
+    else:
+        y = conv(x)
+    return F.gelu(y) if activation == "gelu" else y
+
+
 def dcnv4_corners(p_offset, H, W, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, dilation_h,
                   dilation_w, group, offset_scale, remove_center) -> torch.Tensor:
     """(N,Ho,Wo,G,K,2) int32 corner indices the kernels select (test aid)."""

@@ -193,6 +193,20 @@ int dcnv4b200_linear_ln_fwd(const void* x, const void* weight, const void* bias,
                             int N, int K, void* stream);
 
 /*
+ * y = act(x + bias) over the last dimension of a channels-last tensor, in one pass:
+ *   x, y (rows, C) contiguous in `dtype` (fp16 or bf16; y may alias x), bias (C) in `dtype`,
+ *   C a multiple of 8, activation DCNV4B200_ACT_NONE or DCNV4B200_ACT_GELU (erf form, on the
+ *   sum rounded to `dtype`).
+ * FlashInternImage's stem is conv -> BatchNorm -> GELU -> conv -> BatchNorm
+ * (classification/models/flash_intern_image.py:235-272); once the BatchNorms are folded into
+ * the convolutions for inference, their shift remains as a convolution bias, which PyTorch applies
+ * as a separate broadcast addition followed by a separate GELU kernel.  The reference has no
+ * kernel for this.
+ */
+int dcnv4b200_bias_act_fwd(const void* x, const void* bias, void* y, int dtype, long long rows, int C,
+                           int activation, void* stream);
+
+/*
  * Read and clear the current device's kernel status word (0 = no kernel ever gave up on a
  * bounded wait for its staged tile).  Synchronises the device; meant for tests and
  * post-mortems, not for the hot path.  No counterpart in the reference.

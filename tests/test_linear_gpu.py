@@ -212,3 +212,40 @@ def test_post_norm_layer_scale_models_agree_with_the_stock_path(size):
     assert torch.isfinite(fused).all()
     torch.testing.assert_close(fused.float(), stock.float(), rtol=1e-2, atol=2e-3)
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("rows,C", [(1, 8), (1000, 32), (12544, 64), (333, 80), (7, 768), (100000, 32)])
+def test_bias_act_matches_the_separate_add_and_gelu(rows, C, dtype):
+    from dcnv4_b200 import ops
+    torch.manual_seed(rows + C)
+    x = (torch.randn(rows, C, device=DEV) * 2).to(dtype)
+    b = torch.randn(C, device=DEV).to(dtype)
+    for act in ("none", "gelu"):
+        want = x + b                                   # rounded to the storage type, as the add_ would
+        if act == "gelu":
+            want = F.gelu(want)
+        got = ops.bias_act_(x.clone(), b, act)
+        assert torch.equal(got, want), (act, (got.float() - want.float()).abs().max())
+    assert ops.device_status() == 0
+
+
+def test_folded_stem_uses_bias_act_and_matches_the_stock_path():
+    import copy
+    from dcnv4_b200 import ops
+    from dcnv4_b200.flash_intern_image import flash_intern_image, fold_batchnorm_
+    torch.manual_seed(2)
+    model = fold_batchnorm_(flash_intern_image("t").to(DEV).half().eval())
+    stem = model.patch_embed
+    with torch.no_grad():
+        stem.conv1.bias.normal_(0, 0.5)
+        stem.conv2.bias.normal_(0, 0.5)
+        x = torch.randn(3, 3, 64, 96, device=DEV, dtype=torch.float16)
+        fused = stem(x)
+        ops.FUSED_LINEAR = False
+        try:
+            stock = stem(x)
+        finally:
+            ops.FUSED_LINEAR = True
+    assert fused.shape == stock.shape == (3, 16, 24, 64)
+    torch.testing.assert_close(fused, stock, rtol=2e-3, atol=2e-3)
