@@ -147,6 +147,15 @@ def _single_layer_norm(module) -> Optional[nn.LayerNorm]:
     return None
 
 
+class _ConvAsLinear:
+    """A 1x1 nn.Conv2d seen as the nn.Linear it is (what ops.linear_module_forward reads)."""
+
+    def __init__(self, conv: nn.Conv2d):
+        self.weight = conv.weight.view(conv.out_channels, conv.in_channels)
+        self.bias = conv.bias
+        self.in_features, self.out_features = conv.in_channels, conv.out_channels
+
+
 class MLPLayer(nn.Module):
     def __init__(self, in_features, hidden_features=None, out_features=None, act_layer="GELU",
                  mlp_fc2_bias=False, drop=0.0):
@@ -337,7 +346,16 @@ class FlashInternImage(nn.Module):
         for level in self.levels:
             x, shape = level(x, shape)
         h, w = shape
-        x = self.conv_head(x.view(N, h, w, -1).permute(0, 3, 1, 2))
+        conv, act = self.conv_head[0], self.conv_head[2]
+        if (isinstance(self.conv_head[1][0], nn.Identity) and conv.bias is not None and conv.kernel_size == (1, 1)
+                and conv.stride == (1, 1) and conv.groups == 1 and isinstance(act, nn.GELU)
+                and act.approximate == "none"):
+            # BatchNorm folded (fold_batchnorm_): the 1x1 head convolution is a Linear over the
+            # channels-last tokens, with its bias and the GELU in the same kernel
+            y = ops.linear_module_forward(x.reshape(N * h * w, -1), _ConvAsLinear(conv), None, "gelu")
+            x = y.view(N, h, w, -1).permute(0, 3, 1, 2)
+        else:
+            x = self.conv_head(x.view(N, h, w, -1).permute(0, 3, 1, 2))
         return torch.flatten(self.avgpool(x), 1)
 
     def forward(self, x):
