@@ -435,6 +435,24 @@ int dcnv4b200_linear_ln_fwd(const void* x, const void* weight, const void* bias,
                                 static_cast<cudaStream_t>(stream), gamma, beta, eps, z);
 }
 
+int dcnv4b200_linear_pair_fwd(const void* x, const void* weight, const void* bias, void* y1, int N1, void* y2,
+                              int N2, int dtype, long long M, int K, void* stream) {
+  if (!x || !weight || !y1 || !y2) return DCNV4B200_ERR_NULL;
+  if (dtype != DCNV4B200_F16 && dtype != DCNV4B200_BF16) return DCNV4B200_ERR_DTYPE;
+  if (M < 0 || N1 <= 0 || N2 <= 0 || K <= 0) return DCNV4B200_ERR_SHAPE;
+  // the boundary between the two outputs must fall between two 64-column store units
+  if (N1 % 64 != 0 || N2 % 8 != 0 || K % 8 != 0) return DCNV4B200_ERR_CHANNELS;
+  if (!aligned16(x) || !aligned16(weight) || !aligned16(y1) || !aligned16(y2) || !aligned16(bias))
+    return DCNV4B200_ERR_ALIGN;
+  if (M >= (1LL << 31)) return DCNV4B200_ERR_TOO_LARGE;
+  if (M == 0) return 0;
+  int* status = nullptr;
+  int sms = 1;
+  if (int rc = status_ptr(&status, &sms)) return rc;
+  return (int)launch_linear_fwd(dtype, x, weight, bias, nullptr, y1, M, N1 + N2, K, 0, sms, status,
+                                static_cast<cudaStream_t>(stream), nullptr, nullptr, 0.f, y2, N1);
+}
+
 int dcnv4b200_bias_act_fwd(const void* x, const void* bias, void* y, int dtype, long long rows, int C,
                            int activation, void* stream) {
   if (!x || !bias || !y) return DCNV4B200_ERR_NULL;

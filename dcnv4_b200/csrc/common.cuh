@@ -445,7 +445,7 @@ int layernorm_max_channels(int dtype);
 cudaError_t launch_linear_fwd(int dtype, const void* x, const void* w, const void* bias, const void* residual,
                               void* y, long long M, int N, int K, int act, int sms, int* status,
                               cudaStream_t stream, const void* gamma = nullptr, const void* beta = nullptr,
-                              float eps = 0.f, void* z = nullptr);
+                              float eps = 0.f, void* z = nullptr, int n_split = 0);
 
 // y = act(x + bias) over the channels of a channels-last 16-bit tensor (bias_act.cu).
 cudaError_t launch_bias_act_fwd(int dtype, const void* x, const void* bias, void* y, long long rows, int C, int act,

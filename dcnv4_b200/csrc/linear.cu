@@ -90,6 +90,7 @@ struct LinearParams {
   const void* gamma;     // LayerNorm epilogue (ACT == 2): weight, bias (N), eps
   const void* beta;
   float eps;
+  int n_split;           // > 0 (ACT == 0 only): columns [n_split, N) go to a second tensor (map_z)
   void* y;
   int* status;
 };
@@ -450,7 +451,8 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         __syncwarp();
         PROF_ADD(8);
         if (lane == 0) {
-          tma_store_2d(&map_y, buf, col0, row0);
+          if (ACT == 0 && p.n_split > 0 && col0 >= p.n_split) tma_store_2d(&map_z, buf, col0 - p.n_split, row0);
+          else tma_store_2d(&map_y, buf, col0, row0);
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
         PROF_ADD(9);
@@ -596,9 +598,9 @@ cudaError_t launch_act(const LinearArgs& a, LinearParams p, int sms, cudaStream_
   CUtensorMap mx, mw, my, mr, mz;
   constexpr int UW = unit_cols<BN>();
   if (!make_map(&mx, a.dtype, a.x, p.M, p.K, kBM, kBK) || !make_map(&mw, a.dtype, a.w, p.N, p.K, BN, kBK) ||
-      !make_map(&my, a.dtype, a.y, p.M, p.N, 32, UW) ||
-      !make_map(&mr, a.dtype, a.residual ? a.residual : a.y, p.M, p.N, 32, UW) ||
-      !make_map(&mz, a.dtype, a.z ? a.z : a.y, p.M, p.N, 32, UW))
+      !make_map(&my, a.dtype, a.y, p.M, p.n_split > 0 ? p.n_split : p.N, 32, UW) ||
+      !make_map(&mr, a.dtype, a.residual ? a.residual : a.y, p.M, p.n_split > 0 ? p.n_split : p.N, 32, UW) ||
+      !make_map(&mz, a.dtype, a.z ? a.z : a.y, p.M, p.n_split > 0 ? p.N - p.n_split : p.N, 32, UW))
     return cudaErrorNotSupported;
   p.n_tiles = (p.N + BN - 1) / BN;
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
@@ -627,10 +629,12 @@ cudaError_t launch_bn(int bn, int act, const LinearArgs& a, const LinearParams& 
 }  // namespace
 
 // dtype: 1 fp16, 2 bf16.  Returns cudaErrorNotSupported when the driver lacks tensor maps.
-// act 2 (LayerNorm as second output z; N <= 256) needs gamma, beta, eps and z.
+// act 2 (LayerNorm as second output z; N <= 256) needs gamma, beta, eps and z.  With act 0 and
+// n_split > 0 (a multiple of 64) the columns [n_split, N) are written to z as an (M, N - n_split) tensor
+// and y is (M, n_split): two Linear layers over the same input in one product.
 cudaError_t launch_linear_fwd(int dtype, const void* x, const void* w, const void* bias, const void* residual,
                               void* y, long long M, int N, int K, int act, int sms, int* status,
-                              cudaStream_t stream, const void* gamma, const void* beta, float eps, void* z) {
+                              cudaStream_t stream, const void* gamma, const void* beta, float eps, void* z, int n_split) {
   // Tile width: the widest of 256/128/64 that N fills, unless a narrower one wastes less of the
   // last wave of CTAs (cost model: waves x (columns + fixed per-tile overhead)).
   const int m_tiles = (int)((M + kBM - 1) / kBM);
@@ -653,7 +657,7 @@ cudaError_t launch_linear_fwd(int dtype, const void* x, const void* w, const voi
   p.n_tiles = 0;
   p.k_blocks = (K + kBK - 1) / kBK;
   p.bias = bias; p.residual = residual; p.y = y; p.status = status;
-  p.gamma = gamma; p.beta = beta; p.eps = eps;
+  p.gamma = gamma; p.beta = beta; p.eps = eps; p.n_split = n_split;
   const LinearArgs a{dtype, x, w, residual, y, z};
   if (dtype == 1) return launch_bn<__half>(bn, act, a, p, sms, stream);
   return launch_bn<__nv_bfloat16>(bn, act, a, p, sms, stream);

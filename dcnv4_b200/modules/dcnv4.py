@@ -86,16 +86,29 @@ class DCNv4(nn.Module):
         else:
             H, W = int(L ** 0.5), int(L ** 0.5)
 
-        x = input
-        if not self.without_pointwise:
-            x = self.value_proj(x)
-        x = x.reshape(N, H, W, -1)
-        if self.dw_kernel_size is not None:
-            offset_mask_input = self.offset_mask_dw(input.view(N, H, W, C).permute(0, 3, 1, 2))
-            offset_mask_input = offset_mask_input.permute(0, 2, 3, 1).view(N, L, C)
+        paired = None
+        if not self.without_pointwise and self.dw_kernel_size is None:
+            # both projections read the layer input: at inference they are one tensor-core product
+            paired = self.__dict__.get("_paired_proj")
+            if paired is None or paired.first is not self.value_proj or paired.second is not self.offset_mask:
+                paired = self.__dict__["_paired_proj"] = ops.PairedLinear(self.value_proj, self.offset_mask)
+            if not (input.is_contiguous() and paired.usable(input)):
+                paired = None
+        if paired is not None:
+            x, offset_mask = paired(input)
+            x = x.reshape(N, H, W, -1)
+            offset_mask = offset_mask.reshape(N, H, W, -1)
         else:
-            offset_mask_input = input
-        offset_mask = self.offset_mask(offset_mask_input).reshape(N, H, W, -1)
+            x = input
+            if not self.without_pointwise:
+                x = self.value_proj(x)
+            x = x.reshape(N, H, W, -1)
+            if self.dw_kernel_size is not None:
+                offset_mask_input = self.offset_mask_dw(input.view(N, H, W, C).permute(0, 3, 1, 2))
+                offset_mask_input = offset_mask_input.permute(0, 2, 3, 1).view(N, L, C)
+            else:
+                offset_mask_input = input
+            offset_mask = self.offset_mask(offset_mask_input).reshape(N, H, W, -1)
 
         x_proj = x
         x = DCNv4Function.apply(

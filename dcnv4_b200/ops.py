@@ -264,6 +264,62 @@ def linear_layer_norm_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optio
     return y, z
 
 
+def linear_pair_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                        n1: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Two Linear layers over the same input in one tensor-core product: `weight` is the two
+    weights stacked along the output dimension, `n1` (a multiple of 64) the first layer's
+    out_features.  Returns (x @ W1.T + b1, x @ W2.T + b2) as two contiguous tensors (forward
+    only; fp16 / bf16)."""
+    _check_tensor(x, "input")
+    _check_tensor(weight, "weight")
+    N, K = weight.shape
+    if x.shape[-1] != K or weight.dtype != x.dtype or not 0 < n1 < N:
+        raise RuntimeError("weight must be (n1 + n2, in_features) in the dtype of the input")
+    if bias is not None:
+        _check_tensor(bias, "bias")
+        if bias.dtype != x.dtype or bias.numel() != N:
+            raise RuntimeError("bias must have n1 + n2 elements in the dtype of the input")
+    M = x.numel() // max(K, 1)
+    y1 = torch.empty(x.shape[:-1] + (n1,), dtype=x.dtype, device=x.device)
+    y2 = torch.empty(x.shape[:-1] + (N - n1,), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().dcnv4b200_linear_pair_fwd(x.data_ptr(), weight.data_ptr(),
+                                                  bias.data_ptr() if bias is not None else None,
+                                                  y1.data_ptr(), n1, y2.data_ptr(), N - n1, _code(x), M, K,
+                                                  _stream(x))
+    _lib.check(rc, "linear_pair_forward")
+    return y1, y2
+
+
+class PairedLinear:
+    """Inference-time cache of two nn.Linear layers that read the same input, stacked for
+    `linear_pair_forward`.  The stacked copy is rebuilt whenever a parameter changed (version
+    counters), moved or changed dtype."""
+
+    def __init__(self, first: "torch.nn.Linear", second: "torch.nn.Linear"):
+        self.first, self.second = first, second
+        self._key, self._weight, self._bias = None, None, None
+
+    def usable(self, x: torch.Tensor) -> bool:
+        a, b = self.first, self.second
+        needs_grad = torch.is_grad_enabled() and (x.requires_grad or a.weight.requires_grad or b.weight.requires_grad)
+        return (FUSED_LINEAR and not needs_grad and not torch.is_autocast_enabled() and linear_supported(x, a.weight)
+                and b.weight.dtype == x.dtype and b.weight.is_cuda and a.in_features == b.in_features
+                and a.in_features <= FUSED_LINEAR_MAX_K and a.out_features % 64 == 0 and b.out_features % 8 == 0
+                and (a.bias is None) == (b.bias is None) and (a.bias is None or a.bias.dtype == x.dtype))
+
+    def __call__(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        a, b = self.first, self.second
+        params = [t for t in (a.weight, b.weight, a.bias, b.bias) if t is not None]
+        key = tuple((t.data_ptr(), t._version, t.dtype, t.device) for t in params)
+        if key != self._key:
+            with torch.no_grad():
+                self._weight = torch.cat([a.weight, b.weight], 0).contiguous()
+                self._bias = None if a.bias is None else torch.cat([a.bias, b.bias], 0).contiguous()
+            self._key = key
+        return linear_pair_forward(x, self._weight, self._bias, a.out_features)
+
+
 def linear_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """True when `linear_forward` covers this input (dtype, size, layout)."""
     if not (x.is_cuda and x.is_contiguous() and x.dtype in (torch.float16, torch.bfloat16) and x.numel() > 0):

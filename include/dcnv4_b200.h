@@ -193,6 +193,18 @@ int dcnv4b200_linear_ln_fwd(const void* x, const void* weight, const void* bias,
                             int N, int K, void* stream);
 
 /*
+ * Two Linear layers over the same input in one product (inference): with weight = [W1; W2]
+ * stacked along the output dimension ((N1 + N2, K) row-major) and bias likewise ((N1 + N2) or NULL),
+ *     y1 = x . W1^T + b1   (M, N1)        y2 = x . W2^T + b2   (M, N2)
+ * are written as two separate contiguous tensors while x is read once.  In the reference's
+ * DCNv4 module both the value projection and the offset/mask projection consume the layer input
+ * (DCNv4_op/DCNv4/modules/dcnv4.py:116-124) as two separate nn.Linear calls.
+ *   fp16 / bf16; N1 a multiple of 64, N2 and K multiples of 8; every pointer 16-byte aligned.
+ */
+int dcnv4b200_linear_pair_fwd(const void* x, const void* weight, const void* bias, void* y1, int N1, void* y2,
+                              int N2, int dtype, long long M, int K, void* stream);
+
+/*
  * y = act(x + bias) over the last dimension of a channels-last tensor, in one pass:
  *   x, y (rows, C) contiguous in `dtype` (fp16 or bf16; y may alias x), bias (C) in `dtype`,
  *   C a multiple of 8, activation DCNV4B200_ACT_NONE or DCNV4B200_ACT_GELU (erf form, on the

@@ -249,3 +249,52 @@ def test_folded_stem_uses_bias_act_and_matches_the_stock_path():
             ops.FUSED_LINEAR = True
     assert fused.shape == stock.shape == (3, 16, 24, 64)
     torch.testing.assert_close(fused, stock, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("M,K,n1,n2", [(3136, 64, 64, 112), (1000, 128, 128, 216), (196, 256, 256, 432),
+                                       (49, 512, 512, 864), (130, 72, 64, 8), (5000, 64, 192, 40)])
+def test_two_linears_in_one_product(M, K, n1, n2, dtype):
+    """value and offset/mask projections of a DCNv4 layer (FlashInternImage-T stage shapes first):
+    each output must equal the single-output kernel's bit for bit."""
+    from dcnv4_b200 import ops
+    torch.manual_seed(M + K + n1)
+    x = torch.randn(M, K, device=DEV).to(dtype)
+    w = (torch.randn(n1 + n2, K, device=DEV) / K ** 0.5).to(dtype)
+    b = torch.randn(n1 + n2, device=DEV).to(dtype)
+    for bias in (b, None):
+        y1, y2 = ops.linear_pair_forward(x, w, bias, n1)
+        assert y1.shape == (M, n1) and y2.shape == (M, n2) and y1.is_contiguous() and y2.is_contiguous()
+        assert torch.equal(y1, ops.linear_forward(x, w[:n1].contiguous(), None if bias is None else bias[:n1].contiguous()))
+        assert torch.equal(y2, ops.linear_forward(x, w[n1:].contiguous(), None if bias is None else bias[n1:].contiguous()))
+    assert ops.device_status() == 0
+
+
+def test_dcnv4_module_pairs_its_projections_and_tracks_weight_updates():
+    from dcnv4_b200 import ops
+    from dcnv4_b200.modules.dcnv4 import DCNv4
+    torch.manual_seed(4)
+    m = DCNv4(channels=64, group=4).to(DEV).half().eval()
+    with torch.no_grad():
+        m.offset_mask.weight.normal_(0, 0.1)
+        m.offset_mask.bias.uniform_(0, 1)
+    x = torch.randn(2, 14 * 14, 64, device=DEV, dtype=torch.float16)
+
+    def both():
+        with torch.no_grad():
+            fused = m(x)
+            ops.FUSED_LINEAR = False
+            try:
+                stock = m(x)
+            finally:
+                ops.FUSED_LINEAR = True
+        return fused, stock
+
+    fused, stock = both()
+    torch.testing.assert_close(fused, stock, **TOL[torch.float16])
+    assert "_paired_proj" in m.__dict__
+    with torch.no_grad():                      # an in-place update must invalidate the stacked copy
+        m.value_proj.weight.mul_(0.5)
+    fused2, stock2 = both()
+    torch.testing.assert_close(fused2, stock2, **TOL[torch.float16])
+    assert not torch.allclose(fused2, fused)
