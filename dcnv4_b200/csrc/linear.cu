@@ -22,7 +22,9 @@
 //                         swizzled staging tile and leaves through a TMA store, which writes
 //                         whole lines and clips the ragged edge of the matrix.  The residual
 //                         tile arrives by TMA load into the same staging tile.  Optionally the
-//                         LayerNorm of the finished row leaves as a second output (ACT == 2).
+//                         LayerNorm of the finished row leaves as a second output (ACT == 2),
+//                         or the columns beyond `n_split` go to a second tensor (two stacked
+//                         layers in one product).
 //                         64-column tiles need only eight of these warps; the other eight then
 //                         form a second set working on the other accumulator.
 // The double-buffered accumulator lets the epilogue of tile i overlap the products of tile
