@@ -649,7 +649,7 @@ cudaError_t launch_linear_fwd(int dtype, const void* x, const void* w, const voi
                                   : (cand == 128 ? (act ? stages<__half, 128, 1>() : stages<__half, 128, 0>()) : 8);
     if (cand > 64 && depth < 3 && (K + kBK - 1) / kBK > depth) continue;
     const long long tiles = (long long)m_tiles * ((N + cand - 1) / cand);
-    const double cost = (double)((tiles + sms - 1) / sms) * (cand + 48);
+    const double cost = (double)((tiles + sms - 1) / sms) * (cand + 96);  // 96: fitted per-tile overhead
     if (cost < best * 0.98) { best = cost; bn = cand; }
   }
   if (act == 2) bn = N > 128 ? 256 : (N > 64 ? 128 : 64);  // a row must lie in one tile
