@@ -57,11 +57,12 @@ fda_bwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
     mbar_init(&bar[1], 1);
   }
   __syncthreads();
-  // this CTA's contiguous share of the tiles (consecutive tiles are spatial neighbours, so
-  // the halo pixels they share are still in this SM's L1); shares differ by at most one tile
-  const int share = n_tiles / (int)gridDim.x, extra = n_tiles % (int)gridDim.x;
-  const int tile_begin = (int)blockIdx.x * share + min((int)blockIdx.x, extra);
-  const int tile_end = tile_begin + share + ((int)blockIdx.x < extra ? 1 : 0);
+  // Tiles are dealt round-robin: at any moment the CTAs work on neighbouring tiles, i.e. on the
+  // same image, so that image's value tensor (and in the backward its fp32 gradient accumulator,
+  // the target of the reductions) is what occupies L2 -- with contiguous shares every CTA would
+  // be in a different image and the working set (all images) would not fit.  Sampling locations
+  // are arbitrary, so unlike DCNv4 there is no L1 locality between neighbouring tiles to keep.
+  const int tile_begin = (int)blockIdx.x, tile_step = (int)gridDim.x, tile_end = n_tiles;
   if (threadIdx.x == 0 && tile_begin < tile_end) issue(tile_begin, 0);
 
   const int LK = p.LK;
@@ -69,9 +70,9 @@ fda_bwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
   const int tpg_shift = 31 - __clz(tpg);
 
   int it = 0;
-  for (int tile = tile_begin; tile < tile_end; ++tile, ++it) {
+  for (int tile = tile_begin; tile < tile_end; tile += tile_step, ++it) {
     const int cur = it & 1;
-    const int next = tile + 1;
+    const int next = tile + tile_step;
     if (threadIdx.x == 0 && next < tile_end) issue(next, cur ^ 1);
     const int q0 = tile * p.tile;
     const int nq_tile = min(p.tile, p.nq - q0);
