@@ -23,7 +23,8 @@ size_t fda_bwd_smem(const FdaParams& p, int elem) {
   return 16 + 2 * span + gsz + (size_t)p.tile * p.G * sizeof(float2);
 }
 
-template <typename T, int V>
+// DETR: 4 levels x 4 points and one chunk per lane as compile-time constants (see fda_fwd.cu).
+template <typename T, int V, bool DETR>
 __global__ void __launch_bounds__(kThreads, DCNB200_BWD_MINB)
 fda_bwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
                const int64_t* __restrict__ starts, const T* __restrict__ sla,
@@ -109,20 +110,22 @@ fda_bwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
       gather_corner<T, V>(go_ptr, active, gy0);
 
       float dot = 0.f;  // sum_t g_t p_t, kept by lane 0 of the pair
-      for (int l = 0; l < p.L; ++l) {
+      const int n_lvl = DETR ? 4 : p.L, n_pts = DETR ? 4 : p.K, n_chunks = DETR ? 1 : p.chunks_b;
+#pragma unroll(DETR ? 4 : 1)
+      for (int l = 0; l < n_lvl; ++l) {
         const int Hl = s_lvl[l * 3], Wl = s_lvl[l * 3 + 1];
         const float Hf = (float)Hl, Wf = (float)Wl;
         const size_t img_off = ((size_t)b * p.Len_in + s_lvl[l * 3 + 2]) * p.C + g * p.D + c * V;
-#pragma unroll 2
-        for (int k = 0; k < p.K; ++k) {
-          const int t = l * p.K + k;
+#pragma unroll(DETR ? 4 : 2)
+        for (int k = 0; k < n_pts; ++k) {
+          const int t = l * n_pts + k;
           const float w_im = fda_coord(to_f32(row[2 * t]), Wf);
           const float h_im = fda_coord(to_f32(row[2 * t + 1]), Hf);
           const float m = __expf(to_f32(row[2 * LK + t]) - stat.x) * stat.y;
           float gx = 0.f, gyv = 0.f, gm = 0.f;
           bool ok = bwd_point<T, V>(value + img_off, gvalue + img_off, Hl, Wl, p.C, Hf, Wf, h_im, w_im, m, active,
                                     gy0, gx, gyv, gm);
-          for (int ci = 1; ci < p.chunks_b; ++ci) {
+          for (int ci = 1; ci < n_chunks; ++ci) {
             const int off = ci * tpg * V;
             float gy[V];
             gather_corner<T, V>(go_ptr + off, active, gy);
@@ -177,9 +180,11 @@ static cudaError_t launch_v(const T* value, const int64_t* shapes, const int64_t
                             const T* gout, float* gvalue, T* gsla, const FdaParams& p, int* status,
                             cudaStream_t s) {
   const size_t smem = fda_bwd_smem(p, sizeof(T));
-  auto kern = fda_bwd_kernel<T, V>;
+  const bool detr = p.L == 4 && p.K == 4 && p.chunks_b == 1;
+  auto kern = detr ? fda_bwd_kernel<T, V, true> : fda_bwd_kernel<T, V, false>;
   int per_sm = 1;
-  cudaError_t e = persistent_ctas_per_sm<fda_bwd_kernel<T, V>>(smem, &per_sm);
+  cudaError_t e = detr ? persistent_ctas_per_sm<fda_bwd_kernel<T, V, true>>(smem, &per_sm)
+                       : persistent_ctas_per_sm<fda_bwd_kernel<T, V, false>>(smem, &per_sm);
   if (e != cudaSuccess) return e;
   const long long n_tiles = ((long long)p.nq + p.tile - 1) / p.tile;
   const long long want = (long long)p.sm_count * per_sm;

@@ -23,7 +23,10 @@ size_t fda_fwd_smem(const FdaParams& p, int elem) {
   return 16 + 2 * span_bytes(p, elem) + (size_t)p.tile * p.G * sizeof(float2);
 }
 
-template <typename T, int V>
+// DETR: the Deformable-DETR configuration (4 levels x 4 points, all channels of a lane in one
+// chunk) as compile-time constants -- the level and point loops unroll fully and the row offsets
+// become immediates; every other configuration takes the generic path of the same kernel.
+template <typename T, int V, bool DETR>
 __global__ void __launch_bounds__(kThreads, DCNB200_FWD_MINB)
 fda_fwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
                const int64_t* __restrict__ starts, const T* __restrict__ sla, T* __restrict__ out,
@@ -97,18 +100,20 @@ fda_fwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
       const T* row = s_row + pr * 3 * LK;
       const float2 stat = s_stat[pr];
 
-      for (int ci = 0; ci < p.chunks; ++ci) {
+      const int n_chunks = DETR ? 1 : p.chunks, n_lvl = DETR ? 4 : p.L, n_pts = DETR ? 4 : p.K;
+      for (int ci = 0; ci < n_chunks; ++ci) {
         const int ch0 = (c + ci * p.tpg) * V;
         float acc[V];
 #pragma unroll
         for (int e = 0; e < V; ++e) acc[e] = 0.f;
-        for (int l = 0; l < p.L; ++l) {
+#pragma unroll(DETR ? 4 : 1)
+        for (int l = 0; l < n_lvl; ++l) {
           const int Hl = s_lvl[l * 3], Wl = s_lvl[l * 3 + 1];
           const float Hf = (float)Hl, Wf = (float)Wl;
           const T* img = value + ((size_t)b * p.Len_in + s_lvl[l * 3 + 2]) * p.C + g * p.D + ch0;
 #pragma unroll 4
-          for (int k = 0; k < p.K; ++k) {
-            const int t = l * p.K + k;
+          for (int k = 0; k < n_pts; ++k) {
+            const int t = l * n_pts + k;
             const float w_im = fda_coord(to_f32(row[2 * t]), Wf);
             const float h_im = fda_coord(to_f32(row[2 * t + 1]), Hf);
             const float m = __expf(to_f32(row[2 * LK + t]) - stat.x) * stat.y;
@@ -138,9 +143,11 @@ template <typename T, int V>
 static cudaError_t launch_v(const T* value, const int64_t* shapes, const int64_t* starts, const T* sla,
                             T* out, const FdaParams& p, int* status, cudaStream_t s) {
   const size_t smem = fda_fwd_smem(p, sizeof(T));
-  auto kern = fda_fwd_kernel<T, V>;
+  const bool detr = p.L == 4 && p.K == 4 && p.chunks == 1;
+  auto kern = detr ? fda_fwd_kernel<T, V, true> : fda_fwd_kernel<T, V, false>;
   int per_sm = 1;
-  cudaError_t e = persistent_ctas_per_sm<fda_fwd_kernel<T, V>>(smem, &per_sm);
+  cudaError_t e = detr ? persistent_ctas_per_sm<fda_fwd_kernel<T, V, true>>(smem, &per_sm)
+                       : persistent_ctas_per_sm<fda_fwd_kernel<T, V, false>>(smem, &per_sm);
   if (e != cudaSuccess) return e;
   const long long n_tiles = ((long long)p.nq + p.tile - 1) / p.tile;
   const long long want = (long long)p.sm_count * per_sm;
