@@ -128,50 +128,99 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- CPU arm
 
-def cpu_pass(tensors):
+def _cpu_model():
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.lower().startswith("model name"):
+                    return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
+def _cpu_callable():
+    """(fwd(t, G), fwd_bwd(t, G), kind): the reference's own pure-PyTorch core, imported unmodified
+    (oracle/ref_core.py), when its file is mounted or installed under oracle/_ref; otherwise the
+    grid_sample restatement of the same algorithm (oracle/torch_core.py)."""
+    a = (3, 3, 1, 1, 1, 1, 1, 1)
+    try:
+        from oracle import ref_core
+        if ref_core.available():
+            core = ref_core.load()
+            return (lambda t, G: ref_core.dcnv4_forward(core, t["value"], t["offset_mask"], *a, G, D, 1.0, 0),
+                    lambda t, G: ref_core.dcnv4_forward_backward(core, t["value"], t["offset_mask"], t["grad_out"],
+                                                                 *a, G, D, 1.0, 0),
+                    "reference")
+    except Exception as exc:  # a broken install must not take the benchmark down
+        _note(f"reference core unavailable ({type(exc).__name__}: {exc}); timing the restatement")
     from oracle import torch_core
-    for t, G in tensors:
-        torch_core.dcnv4_fwd_bwd(t["value"], t["offset_mask"], t["grad_out"],
-                                 3, 3, 1, 1, 1, 1, 1, 1, G, D, 1.0, 0)
+    return (lambda t, G: torch_core.dcnv4_core(t["value"], t["offset_mask"], *a, G, D, 1.0, 0),
+            lambda t, G: torch_core.dcnv4_fwd_bwd(t["value"], t["offset_mask"], t["grad_out"], *a, G, D, 1.0, 0),
+            "port")
+
+
+def _median_time(fn, reps, warm):
+    for _ in range(warm):
+        fn()
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        fn()
+        ts.append(time.perf_counter() - t0)
+    return statistics.median(ts)
 
 
 def cpu_baseline(reps=5, warm=2):
-    """grid_sample-based CPU formulation, fp32, forward + autograd backward, on a bounded sample:
-    the four stage shapes at N=CPU_SAMPLE_N.  Returns (GB/s, ms per pass, threads, description)."""
+    """The reference's pure-PyTorch (grid_sample-based) core on the host cores, fp32, all threads:
+      * the bounded sample of the benchmark step: the four stage shapes at N=CPU_SAMPLE_N, forward +
+        autograd backward -> GB/s of algorithmic bytes (the line's metric);
+      * benchmark configuration 0 (N=2, 56x56x64, G=4, seed 0): forward alone and forward + backward.
+    Returns the `cpu_baseline` object of the JSON line."""
     import torch
     from oracle import inputs as oin
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
+    fwd, fwd_bwd, kind = _cpu_callable()
     tensors, nbytes = [], 0
     for HW, C, G in STAGES:
         tensors.append((oin.dcnv4_inputs(CPU_SAMPLE_N, HW, HW, G, D, seed=HW), G))
         f, b = algorithmic_bytes(CPU_SAMPLE_N, HW, C, G, 4)
         nbytes += f + b
-    for _ in range(warm):
-        cpu_pass(tensors)
-    times = []
-    for _ in range(reps):
-        t0 = time.perf_counter()
-        cpu_pass(tensors)
-        times.append(time.perf_counter() - t0)
-    med = statistics.median(times)
-    desc = (f"4 stage shapes at N={CPU_SAMPLE_N} (1/{N_PER_GPU // CPU_SAMPLE_N} of the batch), fp32 only, "
+
+    def sweep():
+        for t, G in tensors:
+            fwd_bwd(t, G)
+
+    med = _median_time(sweep, reps, warm)
+    t0 = oin.dcnv4_inputs(2, 56, 56, 4, D, seed=0)
+    f0, b0 = algorithmic_bytes(2, 56, 64, 4, 4)
+    with torch.no_grad():
+        fwd_s = _median_time(lambda: fwd(t0, 4), max(reps, 10), warm)
+    fb_s = _median_time(lambda: fwd_bwd(t0, 4), max(reps, 10), warm)
+    name = ("dcnv3_core_pytorch of the reference (classification/ops_dcnv3/functions/dcnv3_func.py), unmodified"
+            if kind == "reference" else "grid_sample restatement of the reference's pure-PyTorch core")
+    desc = (f"{name}; 4 stage shapes at N={CPU_SAMPLE_N} (1/{N_PER_GPU // CPU_SAMPLE_N} of the batch), fp32 only, "
             f"forward + autograd backward, median of {reps} passes")
-    return nbytes / med / 1e9, med * 1e3, torch.get_num_threads(), desc
+    return {"value": nbytes / med / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
+            "sample": desc, "ms_per_pass": med * 1e3, "cpu_model": _cpu_model(),
+            "config0": {"shape": "N=2, 56x56x64, G=4x16, 3x3/s1/p1, fp32, seed 0",
+                        "fwd_ms": fwd_s * 1e3, "fwd_gbs": f0 / fwd_s / 1e9,
+                        "fwd_bwd_ms": fb_s * 1e3, "fwd_bwd_gbs": (f0 + b0) / fb_s / 1e9}}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    gbs, ms, threads, desc = cpu_baseline(reps=max(1, args.steps), warm=max(1, min(args.warmup, 3)))
+    cb = cpu_baseline(reps=max(1, args.steps), warm=max(1, min(args.warmup, 3)))
     line = {
-        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_pass"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": desc},
-        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
-        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": {"workload": WORKLOAD, "sample": cb["sample"]},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
@@ -634,9 +683,7 @@ def run_ours(args):
         if args.case or args.no_e2e:
             line["e2e"] = None
         if world == 1 and not args.no_cpu_baseline and not args.case:
-            gbs, ms, threads, desc = cpu_baseline()
-            line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
-                                    "sample": desc, "ms_per_pass": ms}
+            line["cpu_baseline"] = cpu_baseline()
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line), flush=True)

@@ -396,6 +396,15 @@ cudaError_t launch_dcnv4_fwd(int dtype, const void* value, const void* om, void*
                              const DcnParams& p, int* status, cudaStream_t s);
 cudaError_t launch_dcnv4_bwd(int dtype, const void* value, const void* om, const void* gout,
                              float* gvalue_f32, void* gom, const DcnParams& p, int* status, cudaStream_t s);
+// Spatially tiled variants (value tile and, for the backward, the grad_value tile in shared
+// memory; dcnv4_*_tiled.cu).  `*_applies` says whether the configuration is covered.
+bool dcnv4_bwd_tiled_applies(const DcnParams& p);
+cudaError_t launch_dcnv4_bwd_tiled(int dtype, const void* value, const void* om, const void* gout,
+                                   float* gvalue_f32, void* gom, const DcnParams& p, int* status, cudaStream_t s);
+// Kernel choice for configurations both kernels cover: environment variable DCNV4B200_TILED,
+// read at every call; 1 selects the tiled kernel, anything else (-1 unset, 0) the default one.
+// Meant for A/B measurements and for the tests of the tiled kernel.
+int tiled_override();
 cudaError_t launch_fda_fwd(int dtype, const void* value, const int64_t* shapes, const int64_t* starts,
                            const void* sla, void* out, const FdaParams& p, int* status, cudaStream_t s);
 cudaError_t launch_fda_bwd(int dtype, const void* value, const int64_t* shapes, const int64_t* starts,

@@ -15,6 +15,8 @@
 //    zeros) with coalesced 16-byte stores, so grad_offset_mask needs no memset.
 //  * 2-D query tiles and double-buffered bulk-copy staging as in the forward kernel; persistent
 //    CTAs when there are few tiles, one CTA per tile when there are thousands (see launch_v).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace dcnb200 {
@@ -260,8 +262,20 @@ static cudaError_t launch_t(const T* value, const T* om, const T* gout, float* g
                           : launch_v<T, 4>(value, om, gout, gvalue, gom, p, status, s);
 }
 
+int tiled_override() {
+  const char* e = getenv("DCNV4B200_TILED");
+  return (e && (e[0] == '0' || e[0] == '1') && e[1] == 0) ? e[0] - '0' : -1;
+}
+
 cudaError_t launch_dcnv4_bwd(int dtype, const void* value, const void* om, const void* gout,
                              float* gvalue_f32, void* gom, const DcnParams& p, int* status, cudaStream_t s) {
+  // The shared-memory pre-accumulating kernel (dcnv4_bwd_tiled.cu) is correct but measured about
+  // twice as slow as this one on B200 at every tile size tried, so it is never chosen
+  // automatically; DCNV4B200_TILED=1 selects it for the configurations it covers.
+  if (tiled_override() == 1 && dcnv4_bwd_tiled_applies(p)) {
+    const cudaError_t e = launch_dcnv4_bwd_tiled(dtype, value, om, gout, gvalue_f32, gom, p, status, s);
+    if (e != cudaErrorNotSupported) return e;  // no tensor-map support in the driver: other kernel
+  }
   switch (dtype) {
     case 0: return launch_t((const float*)value, (const float*)om, (const float*)gout, gvalue_f32, (float*)gom, p, status, s);
     case 1: return launch_t((const __half*)value, (const __half*)om, (const __half*)gout, gvalue_f32, (__half*)gom, p, status, s);

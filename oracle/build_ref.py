@@ -7,8 +7,9 @@ The three translation units of the reference's extension (DCNv4_op/src/vision.cp
 DCNv4_op/src/cuda/dcnv4_cuda.cu, DCNv4_op/src/cuda/flash_deform_attn_cuda.cu) are compiled
 where they lie with nvcc and the flags of the reference's setup.py (DCNv4_op/setup.py:40-46),
 plus `-gencode arch=compute_100,code=sm_100`; its own build system is not run (setup.py refuses
-to build without a visible GPU, setup.py:36-48).  No reference source is copied: only the built
-module lands in oracle/_ref/ (git-ignored).  The result is a regular PyTorch extension module
+to build without a visible GPU, setup.py:36-48).  Only oracle/_ref/ (git-ignored) is written: the
+built module, and a byte-for-byte install of the reference's pure-PyTorch core file (the timed CPU
+baseline, see oracle/ref_core.py) -- no reference source enters this repository's history.  The result is a regular PyTorch extension module
 exporting dcnv4_forward/backward and flash_deform_attn_forward/backward
 (DCNv4_op/src/vision.cpp:14-21); `load()` imports it by path.
 """
@@ -27,10 +28,27 @@ NAME = "dcnv4_ref_ext"
 LIB = os.path.join(OUT, NAME + ".so")
 
 
-def build(ref_root: str = "/root/reference", force: bool = False) -> str:
+def install_python_core(ref_root: str) -> str:
+    """Place the reference's pure-PyTorch core file, byte for byte, under oracle/_ref/ (git-ignored)
+    so that the CPU baseline of bench.py is the reference's own code on machines without the checkout."""
+    import shutil
+    try:
+        from . import ref_core
+    except ImportError:  # run as a script: this directory is sys.path[0]
+        import ref_core
+    src = os.path.join(ref_root, ref_core.REL_PATH)
+    if not os.path.isfile(src):
+        raise FileNotFoundError(f"reference core not found at {src}")
+    os.makedirs(OUT, exist_ok=True)
+    shutil.copyfile(src, ref_core.INSTALLED)
+    return ref_core.INSTALLED
+
+
+def build(ref_root: str, force: bool = False) -> str:
     src = os.path.join(ref_root, "DCNv4_op", "src")
     if not os.path.isdir(src):
         raise FileNotFoundError(f"reference sources not found under {src}")
+    install_python_core(ref_root)
     if os.path.exists(LIB) and not force:
         return LIB
     import torch
@@ -82,4 +100,8 @@ def load():
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force="--force" in sys.argv))
+    import ref_core as _rc
+    _root = next((a for a in sys.argv[1:] if not a.startswith("--")), None) or _rc.reference_root()
+    if _root is None:
+        raise SystemExit("usage: build_ref.py /path/to/reference (or set DCNV4_REFERENCE_ROOT)")
+    print(build(_root, force="--force" in sys.argv))

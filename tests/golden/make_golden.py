@@ -6,9 +6,7 @@ Run once, in a container where the reference checkout is available:
 
 It imports the reference's pure-PyTorch core `dcnv3_core_pytorch`
 (classification/ops_dcnv3/functions/dcnv3_func.py:172-220) UNMODIFIED by file
-path, with the compiled `DCNv3` module and the `pkg_resources` version lookup
-stubbed (both are only needed by the CUDA autograd function in that file, which
-is never called here), runs it on seeded inputs, differentiates it with
+path (loader: oracle/ref_core.py), runs it on seeded inputs, differentiates it with
 autograd, and stores inputs and results as small `.npz` fixtures.  The test
 suite then checks the C oracle and the CUDA kernels against these files; the
 reference checkout is not needed at test time.
@@ -20,10 +18,8 @@ packed offset_mask tensor into the core's separate offset / mask arguments.
 """
 from __future__ import annotations
 
-import importlib.util
 import os
 import sys
-import types
 
 import numpy as np
 import torch
@@ -32,47 +28,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 from oracle import inputs as oin  # noqa: E402
-
-
-def load_reference_core(ref_root: str):
-    sys.modules.setdefault("DCNv3", types.ModuleType("DCNv3"))
-    try:
-        import pkg_resources  # noqa: F401
-    except Exception:  # pragma: no cover
-        sys.modules["pkg_resources"] = types.ModuleType("pkg_resources")
-    import pkg_resources
-    real = getattr(pkg_resources, "get_distribution", None)
-
-    class _Dist:
-        version = "1.1"
-
-    def fake(name):
-        if name == "DCNv3":
-            return _Dist()
-        return real(name)
-
-    pkg_resources.get_distribution = fake
-    path = os.path.join(ref_root, "classification/ops_dcnv3/functions/dcnv3_func.py")
-    spec = importlib.util.spec_from_file_location("ref_dcnv3_func", path)
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
-    return mod.dcnv3_core_pytorch
-
-
-def split_packed(om: torch.Tensor, G: int, K: int):
-    N, Ho, Wo, _ = om.shape
-    g = om[..., : G * K * 3].reshape(N, Ho, Wo, G, 3 * K)
-    return (g[..., : 2 * K].reshape(N, Ho, Wo, G * K * 2),
-            g[..., 2 * K:].reshape(N, Ho, Wo, G * K))
-
-
-def repack_grads(goff, gmask, G, K, Ppad):
-    N, Ho, Wo, _ = goff.shape
-    out = torch.zeros(N, Ho, Wo, Ppad, dtype=goff.dtype)
-    out[..., : G * K * 3] = torch.cat(
-        (goff.reshape(N, Ho, Wo, G, 2 * K), gmask.reshape(N, Ho, Wo, G, K)), -1
-    ).reshape(N, Ho, Wo, G * K * 3)
-    return out
+from oracle import ref_core  # noqa: E402
+from oracle.ref_core import repack_grads, split_packed  # noqa: E402
 
 
 # name -> (N,H,W,G,D, kh,kw,sh,sw,ph,pw,dh,dw, offset_scale, remove_center, offset_std, seed)
@@ -108,7 +65,7 @@ def run_case(core, spec, dtype):
 
 def main(ref_root: str):
     torch.set_num_threads(max(1, os.cpu_count() or 1))
-    core = load_reference_core(ref_root)
+    core = ref_core.load(ref_root)
 
     small = {}
     for name, spec in CASES.items():
@@ -148,4 +105,7 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else ref_core.reference_root()
+    if root is None:
+        raise SystemExit("usage: make_golden.py /path/to/reference (or set DCNV4_REFERENCE_ROOT)")
+    main(root)
