@@ -35,6 +35,7 @@ _SIGNATURES = {
     "dcnv4b200_fwd_corners": (_i, [_p, _p, _i] + [_i] * 12 + [_f, _i, _i, _p]),
     "fdab200_fwd_corners": (_i, [_p, _p, _p] + [_i] * 6 + [_p]),
     "dcnv4b200_layernorm_fwd": (_i, [_p, _p, _p, _p, _i, _i, C.c_longlong, _i, _f, _p]),
+    "dcnv4b200_layernorm_act_fwd": (_i, [_p, _p, _p, _p, _i, _i, C.c_longlong, _i, _f, _i, _p]),
     "dcnv4b200_linear_fwd": (_i, [_p, _p, _p, _p, _p, _i, C.c_longlong, _i, _i, _i, _p]),
     "dcnv4b200_bias_act_fwd": (_i, [_p, _p, _p, _i, C.c_longlong, _i, _i, _p]),
     "dcnv4b200_linear_pair_fwd": (_i, [_p, _p, _p, _p, _i, _p, _i, _i, C.c_longlong, _i, _p]),

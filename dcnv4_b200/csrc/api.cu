@@ -382,7 +382,13 @@ int fdab200_fwd_corners(const int64_t* spatial_shapes, const void* sampling_loc_
 
 int dcnv4b200_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, int dtype,
                             int param_dtype, long long rows, int C, float eps, void* stream) {
+  return dcnv4b200_layernorm_act_fwd(x, gamma, beta, y, dtype, param_dtype, rows, C, eps, DCNV4B200_ACT_NONE, stream);
+}
+
+int dcnv4b200_layernorm_act_fwd(const void* x, const void* gamma, const void* beta, void* y, int dtype,
+                                int param_dtype, long long rows, int C, float eps, int activation, void* stream) {
   if (!x || !gamma || !beta || !y) return DCNV4B200_ERR_NULL;
+  if (activation != DCNV4B200_ACT_NONE && activation != DCNV4B200_ACT_GELU) return DCNV4B200_ERR_UNSUPPORTED;
   if (!dtype_ok(dtype) || (param_dtype != DCNV4B200_F32 && param_dtype != dtype)) return DCNV4B200_ERR_DTYPE;
   if (rows < 0 || C <= 0) return DCNV4B200_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(y)) return DCNV4B200_ERR_ALIGN;
@@ -392,7 +398,7 @@ int dcnv4b200_layernorm_fwd(const void* x, const void* gamma, const void* beta, 
   int* status = nullptr;
   int sms = 1;
   if (int rc = status_ptr(&status, &sms)) return rc;
-  return (int)launch_layernorm_fwd(dtype, param_dtype, x, gamma, beta, y, rows, C, eps, sms,
+  return (int)launch_layernorm_fwd(dtype, param_dtype, x, gamma, beta, y, rows, C, eps, activation, sms,
                                    static_cast<cudaStream_t>(stream));
 }
 
@@ -492,6 +498,9 @@ int dcnv4b200_device_status(int* status_out) {
 // once the host application has handed all remaining device memory to its own arena.  Such a
 // caller can supply inputs and outputs, but has nowhere to get the fp32 accumulation buffer
 // that the 16-bit backward needs.  For them the buffer lives inside the library image.
+// (The runtime reserves the array when this module is first loaded on a device -- with lazy
+// loading, at the first call of any entry point there -- so such a host calls
+// dcnv4b200_device_status() once per device at start-up, before it claims the memory.)
 
 namespace {
 

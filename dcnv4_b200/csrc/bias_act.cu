@@ -31,6 +31,8 @@ bias_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restri
     __syncthreads();
   }
   const long long tid = (long long)blockIdx.x * kBiasActThreads + threadIdx.x;
+  pdl_trigger();
+  pdl_wait();  // x is the previous kernel's output, and the bias may have been written by one (a fold, a cast)
   // `active_threads` is a multiple of the slots per row, so a thread's column never changes
   float b[8];
   {
@@ -40,8 +42,6 @@ bias_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restri
 #pragma unroll
     for (int i = 0; i < 4; ++i) { const float2 f = unpack2<T>(r[i]); b[2 * i] = f.x; b[2 * i + 1] = f.y; }
   }
-  pdl_trigger();
-  pdl_wait();  // x is the previous kernel's output
   // Whole warps stay in the loop together (the table GELU votes across the warp): a lane past
   // the end works on a dummy vector and does not store.
   const long long warp_first = tid - (threadIdx.x & 31);

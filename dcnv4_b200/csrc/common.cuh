@@ -40,7 +40,26 @@ constexpr int kMaxLevels = 8;             // FlashDeformAttn levels held in shar
 constexpr int kMaxTileRows = 32;          // rows of a 2-D query tile (one bulk copy per row)
 
 // Device status word values (written by a kernel that gave up on a bounded wait).
-enum : int { kStatusOk = 0, kStatusStageTimeout = 1 };
+enum : int {
+  kStatusOk = 0,
+  kStatusStageTimeout = 1,  // a staged copy never landed within the bounded wait
+  kStatusBadLevels = 2      // a FlashDeformAttn level does not lie inside the flattened value tensor
+};
+
+// FlashDeformAttn level table entry (H, W, first row) from the two int64 device tensors, checked
+// against the flattened length: a level that starts before 0 or ends after Len_in -- a caller-side
+// bug, stale shapes, (W,H) order with the wrong starts -- is replaced by an empty level (H = W = 0,
+// every sample then fails the range test and contributes nothing) and recorded in the status
+// word, so that neither the gathers nor the gradient reductions can leave the tensors.
+__device__ __forceinline__ void load_level(int* dst, const int64_t* shapes, const int64_t* starts, int l,
+                                           int len_in, int* status) {
+  const long long H = shapes[2 * l], W = shapes[2 * l + 1], s0 = starts[l];
+  const bool ok = H >= 0 && W >= 0 && s0 >= 0 && H <= len_in && W <= len_in && H * W <= (long long)len_in - s0;
+  dst[0] = ok ? (int)H : 0;
+  dst[1] = ok ? (int)W : 0;
+  dst[2] = ok ? (int)s0 : 0;
+  if (!ok) atomicExch(status, kStatusBadLevels);
+}
 
 // ----------------------------------------------------------------------------- storage types
 
@@ -447,7 +466,7 @@ inline cudaError_t persistent_ctas_per_sm(size_t smem, int* per_sm) {
 }
 
 cudaError_t launch_layernorm_fwd(int dtype, int param_dtype, const void* x, const void* gamma, const void* beta,
-                                 void* y, long long rows, int C, float eps, int sm_count, cudaStream_t s);
+                                 void* y, long long rows, int C, float eps, int act, int sm_count, cudaStream_t s);
 int layernorm_max_channels(int dtype);
 
 // y = epilogue(x . W^T + bias) on the tensor cores (linear.cu); dtype 1 fp16 / 2 bf16.

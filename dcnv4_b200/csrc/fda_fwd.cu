@@ -46,11 +46,7 @@ fda_fwd_kernel(const T* __restrict__ value, const int64_t* __restrict__ shapes,
     issue_stage(s_buf[buf], sla + (size_t)q0 * rowlen, (uint32_t)(nq_tile * rowlen * sizeof(T)), 1, 0, 0, &bar[buf]);
   };
 
-  if (threadIdx.x < p.L) {
-    s_lvl[threadIdx.x * 3] = (int)shapes[threadIdx.x * 2];
-    s_lvl[threadIdx.x * 3 + 1] = (int)shapes[threadIdx.x * 2 + 1];
-    s_lvl[threadIdx.x * 3 + 2] = (int)starts[threadIdx.x];
-  }
+  if (threadIdx.x < p.L) load_level(&s_lvl[threadIdx.x * 3], shapes, starts, (int)threadIdx.x, p.Len_in, status);
   if (threadIdx.x == 0) {
     mbar_init(&bar[0], 1);
     mbar_init(&bar[1], 1);

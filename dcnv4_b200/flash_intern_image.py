@@ -98,7 +98,10 @@ class DropPath(nn.Module):
 
 
 class StemLayer(nn.Module):
-    """Two stride-2 3x3 convolutions: (N,3,H,W) -> (N,H/4,W/4,C) channels-last."""
+    """Two stride-2 3x3 convolutions: (N,3,H,W) -> (N,H/4,W/4,C) channels-last
+    (classification/models/flash_intern_image.py:235-272).  FlashInternImage builds it with the
+    network's norm layer, LayerNorm (:615-618), so each convolution is followed by a LayerNorm over
+    its channels, the first one also by a GELU."""
 
     def __init__(self, in_chans=3, out_chans=96, act_layer="GELU", norm_layer="BN"):
         super().__init__()
@@ -108,15 +111,31 @@ class StemLayer(nn.Module):
         self.conv2 = nn.Conv2d(out_chans // 2, out_chans, kernel_size=3, stride=2, padding=1)
         self.norm2 = build_norm_layer(out_chans, norm_layer, "channels_first", "channels_last")
 
+    def _fused_norm_act(self, x):
+        """LayerNorm + GELU over the channels of a channels-last activation in one pass (inference):
+        the convolution's (N,C,H,W) result in channels_last memory is the contiguous (N,H,W,C) tensor
+        the kernel wants, and so is its input view for the next convolution."""
+        ln = self.norm1[1] if len(self.norm1) == 3 and isinstance(self.norm1[1], LayerNorm) else None
+        if (ln is None or not isinstance(self.act, nn.GELU) or self.act.approximate != "none"
+                or torch.is_grad_enabled() and (x.requires_grad or ln.weight.requires_grad)
+                or torch.is_autocast_enabled() or not LayerNorm.use_library_kernel):
+            return None
+        t = x.permute(0, 2, 3, 1)
+        if not (t.is_contiguous() and ops.layer_norm_supported(t, ln.weight)):
+            return None
+        return ops.layer_norm_forward(t, ln.weight, ln.bias, ln.eps, "gelu").permute(0, 3, 1, 2)
+
     def forward(self, x):
         x = x.contiguous(memory_format=torch.channels_last)
         if (isinstance(self.norm1[0], nn.Identity) and isinstance(self.norm2[0], nn.Identity)
                 and isinstance(self.act, nn.GELU) and self.act.approximate == "none"):
-            # BatchNorms folded (fold_batchnorm_): their shift is the convolution bias, applied
-            # together with the GELU by one pass over the convolution's output
+            # BatchNorm stem with the norms folded (fold_batchnorm_): their shift is the convolution
+            # bias, applied together with the GELU by one pass over the convolution's output
             x = ops.conv2d_bias_act(x, self.conv1, "gelu")
             return self.norm2(ops.conv2d_bias_act(x, self.conv2, "none")).contiguous()
-        x = self.act(self.norm1(self.conv1(x)))
+        x = self.conv1(x)
+        fused = self._fused_norm_act(x)
+        x = fused if fused is not None else self.act(self.norm1(x))
         return self.norm2(self.conv2(x)).contiguous()
 
 
@@ -301,7 +320,7 @@ class FlashInternImage(nn.Module):
         self.num_levels = len(depths)
         self.channels = channels
         self.num_features = int(channels * 2 ** (self.num_levels - 1))
-        self.patch_embed = StemLayer(in_chans=3, out_chans=channels, act_layer=act_layer, norm_layer="BN")
+        self.patch_embed = StemLayer(in_chans=3, out_chans=channels, act_layer=act_layer, norm_layer=norm_layer)
         self.pos_drop = nn.Dropout(p=drop_rate)
         total = sum(depths)
         dpr = [drop_path_rate * i / max(total - 1, 1) for i in range(total)]
@@ -364,11 +383,11 @@ class FlashInternImage(nn.Module):
 
 @torch.no_grad()
 def fold_batchnorm_(model: "FlashInternImage") -> "FlashInternImage":
-    """Inference-only rewrite, in place: fold the three BatchNorm2d layers of the network (stem
-    conv1/conv2, classification head conv) into the convolutions in front of them, using the
-    running statistics, and replace them by identities.  Saves three full passes over the largest
-    activations of the model.  The model must be in eval mode and is no longer trainable (nor
-    state-dict compatible) afterwards."""
+    """Inference-only rewrite, in place: fold every BatchNorm2d of the network into the convolution
+    in front of it, using the running statistics, and replace it by an identity.  FlashInternImage
+    has one, behind the 1x1 convolution of the classification head (its stem and downsample norms
+    are LayerNorms); a stem built with norm_layer='BN' is folded as well.  The model must be in eval
+    mode and is no longer trainable (nor state-dict compatible) afterwards."""
     if model.training:
         raise RuntimeError("fold_batchnorm_ is for eval-mode models")
 
@@ -380,10 +399,11 @@ def fold_batchnorm_(model: "FlashInternImage") -> "FlashInternImage":
         conv.bias = nn.Parameter(new_bias.to(conv.weight.dtype), requires_grad=False)
 
     stem = model.patch_embed
-    fold(stem.conv1, stem.norm1[0])
-    stem.norm1[0] = nn.Identity()
-    fold(stem.conv2, stem.norm2[0])
-    stem.norm2[0] = nn.Identity()
+    if isinstance(stem.norm1[0], nn.BatchNorm2d) and isinstance(stem.norm2[0], nn.BatchNorm2d):
+        fold(stem.conv1, stem.norm1[0])
+        stem.norm1[0] = nn.Identity()
+        fold(stem.conv2, stem.norm2[0])
+        stem.norm2[0] = nn.Identity()
     fold(model.conv_head[0], model.conv_head[1][0])
     model.conv_head[1][0] = nn.Identity()
     return model

@@ -64,7 +64,23 @@ class DCNv4(nn.Module):
                 torch.tensor(0.0, dtype=torch.float).view((1,)).repeat(group, ))
             self.center_feature_scale_module = CenterFeatureScaleModule()
 
+    def invalidate_fused_weights(self) -> None:
+        """Drop the stacked value/offset-mask weights of the inference path.  Needed only after
+        writing a parameter through `.data`, which PyTorch's version counters do not see."""
+        paired = self.__dict__.get("_paired_proj")
+        if paired is not None:
+            paired.invalidate()
+
+    def train(self, mode: bool = True):
+        self.invalidate_fused_weights()
+        return super().train(mode)
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self.invalidate_fused_weights()
+        return super()._load_from_state_dict(*args, **kwargs)
+
     def _reset_parameters(self):
+        self.invalidate_fused_weights()
         constant_(self.offset_mask.weight.data, 0.)
         constant_(self.offset_mask.bias.data, 0.)
         if not self.without_pointwise:

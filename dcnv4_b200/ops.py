@@ -168,10 +168,14 @@ def flash_deform_attn_backward(value, spatial_shapes, level_start_index, samplin
     return [grad_value, grad_sla]
 
 
-def layer_norm_forward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float) -> torch.Tensor:
+def layer_norm_forward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+                       activation: str = "none") -> torch.Tensor:
     """LayerNorm over the last dimension of a contiguous CUDA tensor with the library's
-    channels-last kernel (forward only; no autograd).  Raises ValueError for sizes the kernel
-    does not cover -- callers that want a fallback check `layer_norm_supported` first."""
+    channels-last kernel (forward only; no autograd), optionally followed by GELU (erf form) in
+    the same pass.  Raises ValueError for sizes the kernel does not cover -- callers that want a
+    fallback check `layer_norm_supported` first."""
+    if activation not in ("none", "gelu"):
+        raise ValueError("activation must be 'none' or 'gelu'")
     _check_tensor(x, "input")
     _check_tensor(weight, "weight")
     _check_tensor(bias, "bias")
@@ -180,9 +184,9 @@ def layer_norm_forward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor
         raise RuntimeError("weight and bias must have the size of the last dimension and one dtype")
     y = torch.empty_like(x)
     with torch.cuda.device(x.device):
-        rc = _lib.lib().dcnv4b200_layernorm_fwd(x.data_ptr(), weight.data_ptr(), bias.data_ptr(), y.data_ptr(),
-                                                _code(x), _code(weight), x.numel() // max(C, 1), C, float(eps),
-                                                _stream(x))
+        rc = _lib.lib().dcnv4b200_layernorm_act_fwd(x.data_ptr(), weight.data_ptr(), bias.data_ptr(), y.data_ptr(),
+                                                    _code(x), _code(weight), x.numel() // max(C, 1), C, float(eps),
+                                                    1 if activation == "gelu" else 0, _stream(x))
     _lib.check(rc, "layer_norm_forward")
     return y
 
@@ -294,10 +298,16 @@ def linear_pair_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[to
 class PairedLinear:
     """Inference-time cache of two nn.Linear layers that read the same input, stacked for
     `linear_pair_forward`.  The stacked copy is rebuilt whenever a parameter changed (version
-    counters), moved or changed dtype."""
+    counters), moved or changed dtype.  Writes through `.data` (`param.data.copy_()` in an EMA
+    update, `constant_(w.data)`) do not bump a version counter: the owning module therefore
+    calls `invalidate()` from `train()`, `_load_from_state_dict()` and `_reset_parameters()`, and
+    code that writes `.data` by other routes must call it too."""
 
     def __init__(self, first: "torch.nn.Linear", second: "torch.nn.Linear"):
         self.first, self.second = first, second
+        self._key, self._weight, self._bias = None, None, None
+
+    def invalidate(self) -> None:
         self._key, self._weight, self._bias = None, None, None
 
     def usable(self, x: torch.Tensor) -> bool:

@@ -46,6 +46,10 @@ enum {
   DCNV4B200_ERR_SCRATCH_LIMIT = -10 /* tensor larger than the built-in scratch of *_static_scratch */
 };
 
+/* Activation codes of the fused kernels around the operator. */
+#define DCNV4B200_ACT_NONE 0
+#define DCNV4B200_ACT_GELU 1
+
 /* Version of this ABI (DCNV4B200_ABI_VERSION of the build). */
 int dcnv4b200_abi_version(void);
 
@@ -159,6 +163,18 @@ int dcnv4b200_layernorm_fwd(const void* x, const void* gamma, const void* beta, 
                             int param_dtype, long long rows, int C, float eps, void* stream);
 
 /*
+ * LayerNorm followed by an activation in the same pass: y = act(LayerNorm(x)), with the normalised
+ * value rounded to `dtype` before the activation, as a separate LayerNorm and GELU pair would.
+ * FlashInternImage's stem is conv -> LayerNorm -> GELU -> conv -> LayerNorm over the largest
+ * activations of the network (classification/models/flash_intern_image.py:235-272, built with
+ * norm_layer='LN' at :615-618); the reference runs the norm and the activation as two kernels.
+ * `activation` is DCNV4B200_ACT_NONE or DCNV4B200_ACT_GELU (erf form); other arguments and limits
+ * as dcnv4b200_layernorm_fwd.
+ */
+int dcnv4b200_layernorm_act_fwd(const void* x, const void* gamma, const void* beta, void* y, int dtype,
+                                int param_dtype, long long rows, int C, float eps, int activation, void* stream);
+
+/*
  * Linear layer with a fused epilogue, inference only, on the tcgen05 tensor cores:
  *     t = x . weight^T + bias            rounded to `dtype` (what nn.Linear would store)
  *     t = GELU(t)                        if activation == DCNV4B200_ACT_GELU (erf form)
@@ -171,8 +187,6 @@ int dcnv4b200_layernorm_fwd(const void* x, const void* gamma, const void* beta, 
  *   (DCNV4B200_ERR_DTYPE otherwise).  N and K must be multiples of 8 (_ERR_CHANNELS), every
  *   pointer 16-byte aligned.  y may alias residual; it must not alias x.
  */
-#define DCNV4B200_ACT_NONE 0
-#define DCNV4B200_ACT_GELU 1
 int dcnv4b200_linear_fwd(const void* x, const void* weight, const void* bias, const void* residual, void* y,
                          int dtype, long long M, int N, int K, int activation, void* stream);
 
@@ -219,9 +233,12 @@ int dcnv4b200_bias_act_fwd(const void* x, const void* bias, void* y, int dtype, 
                            int activation, void* stream);
 
 /*
- * Read and clear the current device's kernel status word (0 = no kernel ever gave up on a
- * bounded wait for its staged tile).  Synchronises the device; meant for tests and
- * post-mortems, not for the hot path.  No counterpart in the reference.
+ * Read and clear the current device's kernel status word: 0 = nothing to report; 1 = a kernel
+ * gave up on a bounded wait for its staged tile; 2 = a FlashDeformAttn call was given a level
+ * (spatial_shapes / level_start_index) that does not lie inside the flattened value tensor --
+ * that level was treated as empty, its samples contributing nothing, instead of being read or
+ * written out of bounds (the reference trusts these device tensors unchecked).  Synchronises the
+ * device; meant for tests and post-mortems, not for the hot path.  No counterpart in the reference.
  */
 int dcnv4b200_device_status(int* status_out);
 
@@ -244,8 +261,13 @@ int dcnv4b200_device_status(int* status_out);
  *    (4 Mi elements = 16 MiB of fp32, held by every GPU that loads the library until the
  *    process exits); larger tensors return DCNV4B200_ERR_SCRATCH_LIMIT and launch nothing.
  *    fp32 tensors accumulate in grad_value itself and have no size limit.
- *  - The first call on a device looks up the array's device address (one cheap runtime
- *    query, no allocation); make that first call outside any stream capture.
+ *  - The first call on a device looks up the array's device address; make that first call
+ *    outside any stream capture.  The 16 MiB themselves are reserved by the CUDA runtime when
+ *    this library's device code is first loaded on a device, which with lazy module loading
+ *    (the default) happens at the first call of ANY entry point that touches the device.  A
+ *    host that later hands all remaining device memory to its own arena should therefore make
+ *    one call per device at start-up -- dcnv4b200_device_status() is enough -- BEFORE it claims
+ *    the memory; after that no call of this entry point changes the amount of free memory.
  *  - All calls on a device share the one array.  Each call clears the part it uses before
  *    summing into it, so calls issued one after another on a stream are fine; calls that may
  *    overlap on the GPU (different streams, different host threads) race on it and must be

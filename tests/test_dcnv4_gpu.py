@@ -245,6 +245,12 @@ def test_autograd_function_and_module():
 
 
 def test_module_variants_match_composition():
+    """The S/B/L-style module configuration (depthwise conv before the offset/mask Linear, centre-feature
+    scale, remove_center, offset_scale 2) equals its parts composed around the oracle:
+    value_proj / dw-conv + offset_mask Linear -> operator -> sigmoid blend -> output_proj
+    (DCNv4_op/DCNv4/modules/dcnv4.py:116-152)."""
+    import torch.nn.functional as F
+
     import dcnv4_b200
     torch.manual_seed(1)
     mod = dcnv4_b200.DCNv4(channels=64, group=4, dw_kernel_size=3, center_feature_scale=True,
@@ -252,14 +258,35 @@ def test_module_variants_match_composition():
     assert mod.offset_mask.out_features == 96 and mod.output_proj.bias is None
     with torch.no_grad():
         mod.offset_mask.weight.normal_(0, 0.1)
+        mod.offset_mask.bias.uniform_(0, 1)
         mod.center_feature_scale_proj_weight.normal_(0, 0.1)
-    x = torch.randn(1, 12 * 10, 64, device=DEV)
-    y = mod(x, shape=(12, 10))
-    assert y.shape == x.shape and torch.isfinite(y).all()
+        mod.center_feature_scale_proj_bias.normal_(0, 0.5)
+    H, W = 12, 10
+    x = torch.randn(2, H * W, 64, device=DEV)
+    with torch.no_grad():
+        y = mod(x, shape=(H, W))
+        assert y.shape == x.shape
+        xv = mod.value_proj(x).reshape(2, H, W, 64)
+        dw = mod.offset_mask_dw(x.view(2, H, W, 64).permute(0, 3, 1, 2)).permute(0, 2, 3, 1).reshape(2, H * W, 64)
+        omv = mod.offset_mask(dw).reshape(2, H, W, 96)
+        core = cref.dcnv4_forward(xv.cpu(), omv.cpu(), 3, 3, 1, 1, 1, 1, 1, 1, 4, 16, 2.0, 1).to(DEV).float()
+        scale = F.linear(core, mod.center_feature_scale_proj_weight, mod.center_feature_scale_proj_bias).sigmoid()
+        scale = scale[..., None].repeat(1, 1, 1, 1, 16).flatten(-2)
+        blended = core * (1 - scale) + xv * scale
+        ref = mod.output_proj(blended.reshape(2, H * W, 64))
+    close(y, ref, dict(rtol=1e-3, atol=1e-4), "module with dw conv, centre-feature scale, remove_center")
+    # the blend must matter in this test (scale is not ~0 or ~1 everywhere)
+    assert 0.2 < float(scale.mean()) < 0.8 and float((blended - core).abs().max()) > 0.1
     sd = mod.state_dict()
     for k in ("offset_mask.weight", "offset_mask_dw.weight", "value_proj.weight", "output_proj.weight",
               "center_feature_scale_proj_weight", "center_feature_scale_proj_bias"):
         assert k in sd
+    # and its gradients flow through every part
+    xg = x.clone().requires_grad_(True)
+    mod(xg, shape=(H, W)).square().mean().backward()
+    for prm in (mod.offset_mask_dw.weight, mod.offset_mask.weight, mod.value_proj.weight,
+                mod.center_feature_scale_proj_weight):
+        assert prm.grad is not None and float(prm.grad.abs().sum()) > 0
 
 
 def test_argument_errors():

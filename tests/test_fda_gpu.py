@@ -149,3 +149,36 @@ def test_argument_errors():
         nine = torch.ones(9, 2, dtype=torch.int64, device=DEV)
         ops.flash_deform_attn_forward(torch.zeros(1, 9, 1, 8, device=DEV), nine, torch.arange(9, device=DEV),
                                       torch.zeros(1, 1, 1, 27, device=DEV), 64, 1)
+
+
+def test_level_outside_the_value_tensor_is_ignored_and_reported():
+    """A level whose start + H*W exceeds Len_in (stale shapes, a caller-side bug) must not be read or
+    written: the kernels treat it as empty -- its samples contribute nothing, softmax weights as if
+    they were there -- and record status 2.  The reference trusts these device tensors unchecked."""
+    from dcnv4_b200 import ops
+    K = 4
+    t = oin.fda_inputs(2, ((6, 8), (3, 4)), 2, 16, K, Len_q=37, seed=9, dtype=torch.float32, device=DEV)
+    assert ops.device_status() == 0
+    bad_shapes = t["spatial_shapes"].clone()
+    bad_shapes[1] = torch.tensor([30, 40])            # 1200 positions claimed, 12 exist
+    out = ops.flash_deform_attn_forward(t["value"], bad_shapes, t["level_start_index"], t["sampling_loc_attn"], 64, K)
+    gv, gs = ops.flash_deform_attn_backward(t["value"], bad_shapes, t["level_start_index"], t["sampling_loc_attn"],
+                                            t["grad_out"], 64, K)
+    assert ops.device_status() == 2
+    assert ops.device_status() == 0                   # read-and-clear
+    # same thing said legally: the true shapes, level 1's points moved far outside the map
+    sla = t["sampling_loc_attn"].clone()
+    sla[..., 2 * K: 4 * K] = -5.0
+    ref_out = cref.fda_forward(t["value"].cpu(), t["spatial_shapes"].cpu(), t["level_start_index"].cpu(), sla.cpu(), K)
+    ref_gv, ref_gs = cref.fda_backward(t["value"].cpu(), t["spatial_shapes"].cpu(), t["level_start_index"].cpu(),
+                                       sla.cpu(), t["grad_out"].cpu(), K)
+    close(out, ref_out, FWD_TOL[torch.float32], "forward")
+    close(gv, ref_gv, BWD_TOL[torch.float32], "grad_value")
+    assert float(gv[:, 48:].abs().max()) == 0.0       # nothing was added to the rows of the bad level
+    tol = dict(BWD_TOL[torch.float32]); tol["atol"] *= 8
+    close(gs, ref_gs, tol, "grad_sampling_loc_attn")
+    # a negative start is caught the same way
+    bad_starts = t["level_start_index"].clone()
+    bad_starts[0] = -3
+    ops.flash_deform_attn_forward(t["value"], t["spatial_shapes"], bad_starts, t["sampling_loc_attn"], 64, K)
+    assert ops.device_status() == 2

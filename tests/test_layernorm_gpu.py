@@ -27,6 +27,45 @@ def test_layernorm_matches_fp32_reference(rows, C, dtype):
         torch.testing.assert_close(y.float(), ref, **tol)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16], ids=["fp32", "fp16", "bf16"])
+@pytest.mark.parametrize("rows,C", [(5, 32), (4099, 32), (777, 64), (33, 320)])
+def test_layernorm_with_gelu_matches_the_two_step_formulation(rows, C, dtype):
+    """y = GELU(LayerNorm(x)) in one pass equals LayerNorm (rounded to the storage type) followed by GELU."""
+    from dcnv4_b200 import ops
+    torch.manual_seed(rows + C)
+    x = (torch.randn(rows, C, device=DEV) * 2 - 0.5).to(dtype)
+    w, b = torch.randn(C, device=DEV).to(dtype), torch.randn(C, device=DEV).to(dtype)
+    y = ops.layer_norm_forward(x, w, b, 1e-6, "gelu")
+    ref = F.gelu(F.layer_norm(x.float(), (C,), w.float(), b.float(), 1e-6).to(dtype).float())
+    tol = {torch.float32: dict(rtol=1e-5, atol=1e-5), torch.float16: dict(rtol=2e-3, atol=2e-3),
+           torch.bfloat16: dict(rtol=1.6e-2, atol=1.6e-2)}[dtype]
+    torch.testing.assert_close(y.float(), ref, **tol)
+    with pytest.raises(ValueError):
+        ops.layer_norm_forward(x, w, b, 1e-6, "relu")
+
+
+def test_stem_layer_fused_norm_matches_the_stock_modules():
+    """FlashInternImage's stem (conv -> LayerNorm -> GELU -> conv -> LayerNorm) with the fused
+    LayerNorm+GELU pass equals the same modules run one by one."""
+    from dcnv4_b200.flash_intern_image import LayerNorm, StemLayer
+    torch.manual_seed(3)
+    stem = StemLayer(3, 64, "GELU", "LN").to(DEV).half().eval()
+    with torch.no_grad():
+        for ln in (stem.norm1[1], stem.norm2[1]):
+            ln.weight.uniform_(0.5, 1.5)
+            ln.bias.normal_(0, 0.3)
+        x = torch.randn(4, 3, 64, 96, device=DEV).half()
+        fast = stem(x)
+        LayerNorm.use_library_kernel = False
+        try:
+            slow = stem(x)
+        finally:
+            LayerNorm.use_library_kernel = True
+    assert fast.shape == (4, 16, 24, 64) and fast.is_contiguous()
+    torch.testing.assert_close(fast.float(), slow.float(), rtol=2e-2, atol=2e-2)
+    assert stem.state_dict().keys() >= {"norm1.1.weight", "norm1.1.bias", "norm2.1.weight", "norm2.1.bias"}
+
+
 def test_layernorm_module_falls_back_when_autograd_needs_it():
     from dcnv4_b200.flash_intern_image import LayerNorm
     ln = LayerNorm(64, eps=1e-6).to(DEV)

@@ -15,7 +15,7 @@ def test_parameter_counts_match_the_published_model_sizes(size, millions):
 def test_state_dict_keys_follow_the_reference_naming():
     m = flash_intern_image("s")
     keys = set(m.state_dict())
-    for k in ("patch_embed.conv1.weight", "patch_embed.norm1.0.running_mean", "patch_embed.norm2.0.weight",
+    for k in ("patch_embed.conv1.weight", "patch_embed.norm1.1.weight", "patch_embed.norm2.1.bias",
               "levels.0.blocks.0.norm1.0.weight", "levels.0.blocks.0.dcn.offset_mask.weight",
               "levels.0.blocks.0.dcn.offset_mask_dw.weight", "levels.0.blocks.0.dcn.value_proj.bias",
               "levels.0.blocks.0.dcn.output_proj.weight", "levels.0.blocks.0.gamma1", "levels.0.blocks.0.mlp.fc1.weight",
@@ -103,3 +103,33 @@ def test_layers_chain_their_layernorms_without_changing_the_result():
         want = blk.norm(want)
     torch.testing.assert_close(got, want)
     assert isinstance(blk.blocks[0], layer_cls)
+
+
+@pytest.mark.parametrize("size", ["t", "s", "b", "l"])
+def test_state_dict_matches_the_reference_model_key_for_key(size):
+    """Every parameter / buffer name and shape of the reference's own FlashInternImage
+    (classification/models/flash_intern_image.py:235-770, built with the released settings; fixture
+    written by tests/golden/make_state_dict_fixture.py) exists here with the same shape, and nothing
+    else does: a released checkpoint loads with strict=True."""
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(__file__), "golden", "flash_intern_image_state_dicts.json")) as f:
+        want = json.load(f)[size]
+    got = {k: list(v.shape) for k, v in flash_intern_image(size).state_dict().items()}
+    assert set(got) == set(want), (sorted(set(want) - set(got))[:5], sorted(set(got) - set(want))[:5])
+    bad = [k for k in want if got[k] != want[k]]
+    assert not bad, [(k, got[k], want[k]) for k in bad[:5]]
+
+
+def test_fused_projection_cache_is_dropped_when_parameters_may_have_changed_unseen():
+    """The stacked value/offset-mask weights are keyed on version counters, which writes through
+    `.data` bypass; train(), load_state_dict() and _reset_parameters() drop the cache."""
+    from dcnv4_b200 import DCNv4, ops
+    mod = DCNv4(channels=64, group=4)
+    paired = mod.__dict__["_paired_proj"] = ops.PairedLinear(mod.value_proj, mod.offset_mask)
+    for action in (lambda: mod.train(False), lambda: mod.load_state_dict(mod.state_dict()),
+                   mod._reset_parameters, mod.invalidate_fused_weights):
+        paired._key = ("stale",)
+        paired._weight = torch.zeros(1)
+        action()
+        assert paired._key is None and paired._weight is None

@@ -7,11 +7,18 @@ the application has claimed the memory); it keeps its fp32 accumulation buffer i
 array inside the library.  Two calls in a row with different inputs check that the shared
 array is cleared between calls; this file is named so that it is collected after every other
 test and also passes when run alone in a fresh process.
+
+On "allocates nothing": the 16 MiB array is part of the library's device image, which the CUDA
+runtime places on a device when the library's code is first loaded there (with lazy loading, at
+the first call of any entry point).  A host that claims all device memory for itself therefore
+touches the library once per device at start-up; from then on a call of the entry point leaves
+the amount of free device memory exactly as it was, which the third test measures.
 """
 import pytest
 import torch
 
 from dcnv4_b200 import _lib
+from oracle import cref
 from tests.util import BWD_TOL
 
 pytestmark = pytest.mark.gpu
@@ -19,15 +26,19 @@ DEV = "cuda"
 
 
 def _inputs(seed, dtype, N=3, HW=14, G=4, D=16):
+    return _inputs_hw(seed, dtype, N, HW, HW, G, D)
+
+
+def _inputs_hw(seed, dtype, N, H, W, G, D):
     g = torch.Generator().manual_seed(seed)
     K, C = 9, G * D
     P = -(-3 * G * K // 8) * 8
-    value = torch.randn(N, HW, HW, C, generator=g)
-    om = torch.zeros(N, HW, HW, P)
-    om[..., : 3 * G * K] = torch.cat((torch.randn(N, HW, HW, G, 2 * K, generator=g),
-                                      torch.rand(N, HW, HW, G, K, generator=g)), -1).reshape(N, HW, HW, -1)
-    gout = torch.randn(N, HW, HW, C, generator=g)
-    return [x.to(device=DEV, dtype=dtype) for x in (value, om, gout)], (N, HW, HW, G, D, P)
+    value = torch.randn(N, H, W, C, generator=g)
+    om = torch.zeros(N, H, W, P)
+    om[..., : 3 * G * K] = torch.cat((torch.randn(N, H, W, G, 2 * K, generator=g),
+                                      torch.rand(N, H, W, G, K, generator=g)), -1).reshape(N, H, W, -1)
+    gout = torch.randn(N, H, W, C, generator=g)
+    return [x.to(device=DEV, dtype=dtype) for x in (value, om, gout)], (N, H, W, G, D, P)
 
 
 def _scalars(dims):
@@ -68,6 +79,51 @@ def test_static_scratch_backward_matches_workspace_backward_twice(dtype, code):
         assert torch.equal(got_gom, want_gom), f"call {call}: grad_offset_mask differs"
         # grad_value is summed with atomics in both entry points: same tolerance as the parity tests
         torch.testing.assert_close(got_gv.double(), want_gv.double(), **BWD_TOL[dtype])
+        # and against the CPU oracle, on the values the GPU saw
+        N, H, W, G, D, _ = dims
+        ref_gv, ref_gom = cref.dcnv4_backward(value.float().cpu(), om.float().cpu(), gout.float().cpu(),
+                                              3, 3, 1, 1, 1, 1, 1, 1, G, D, 1.0, 0)
+        torch.testing.assert_close(got_gv.double().cpu(), ref_gv, **BWD_TOL[dtype])
+        torch.testing.assert_close(got_gom.double().cpu(), ref_gom, **BWD_TOL[dtype])
+
+
+def test_static_scratch_call_leaves_free_memory_unchanged():
+    """After the library has been used once on the device (module loaded, array address known), a call of
+    the allocation-free entry point must not change the amount of free device memory."""
+    lib = _lib.lib()
+    (value, om, gout), dims = _inputs(303, torch.float16)
+    _static_entry(lib, _lib.F16, value, om, gout, dims)           # first use on this device
+    gv, gom = torch.empty_like(value), torch.empty_like(om)       # outputs allocated before the measurement
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    rc = lib.dcnv4b200_bwd_static_scratch(value.data_ptr(), om.data_ptr(), gout.data_ptr(), gv.data_ptr(),
+                                          gom.data_ptr(), _lib.F16, *_scalars(dims),
+                                          torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert rc == 0
+    assert free_after == free_before
+
+
+def test_static_scratch_exactly_at_the_limit_and_one_row_beyond():
+    """1 x 256 x 256 x (4 groups x 16) fp16 is exactly 4 Mi elements: the whole array is cleared, summed into
+    and converted, its last element included.  One more pixel row is refused."""
+    lib = _lib.lib()
+    limit = lib.dcnv4b200_bwd_static_scratch_max_elements()
+    (value, om, gout), dims = _inputs_hw(404, torch.float16, 1, 256, 256, 4, 16)
+    assert value.numel() == limit
+    want_gv, want_gom = _reference_entry(lib, _lib.F16, value, om, gout, dims)
+    got_gv, got_gom = _static_entry(lib, _lib.F16, value, om, gout, dims)
+    torch.cuda.synchronize()
+    assert torch.equal(got_gom, want_gom)
+    torch.testing.assert_close(got_gv.double(), want_gv.double(), **BWD_TOL[torch.float16])
+    assert float(got_gv[0, -1, -1].abs().sum()) > 0               # the array's tail was used
+    (value, om, gout), dims = _inputs_hw(405, torch.float16, 1, 257, 256, 4, 16)
+    gv, gom = torch.empty_like(value), torch.empty_like(om)
+    rc = lib.dcnv4b200_bwd_static_scratch(value.data_ptr(), om.data_ptr(), gout.data_ptr(), gv.data_ptr(),
+                                          gom.data_ptr(), _lib.F16, *_scalars(dims),
+                                          torch.cuda.current_stream().cuda_stream)
+    assert rc == -10
 
 
 def test_static_scratch_rejects_oversized_tensors():
@@ -82,5 +138,3 @@ def test_static_scratch_rejects_oversized_tensors():
                                           3, 3, 1, 1, 1, 1, 1, 1, 1.0, 0, 112, 0, None)
     assert rc == -10
     assert b"scratch" in lib.dcnv4b200_strerror(rc)
-    # exactly at the limit is accepted by the size check (1 x 256 x 256 x 64 = 4 Mi)
-    assert 1 * 256 * 256 * 64 == limit
