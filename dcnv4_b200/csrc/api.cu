@@ -99,16 +99,17 @@ int lane_geometry(P& p, int D, int dtype, bool wide_fwd, bool wide_bwd) {
 // 2-D query tile of one CTA for the DCNv4 kernels: at most `max_q` queries (what fits the
 // shared-memory budget, capped so that a CTA keeps a few items per thread), as square as the
 // divisors of the output size allow, and small enough to leave several tiles per SM.
-void pick_tile_2d(int N, int Ho, int Wo, size_t bytes_per_query, int items_per_query, int* th, int* tw) {
+void pick_tile_2d(int N, int Ho, int Wo, size_t bytes_per_query, int items_per_query, int sm_count, int* th, int* tw) {
   // The search below is pure arithmetic on its arguments; a small per-thread memo keeps it off
   // the per-call path of a training loop that repeats the same few shapes.
-  struct Memo { int N, Ho, Wo, ipq; size_t bpq; int th, tw; };
+  struct Memo { int N, Ho, Wo, ipq, sms; size_t bpq; int th, tw; };
   constexpr int kMemo = 16;
   thread_local Memo memo[kMemo] = {};
   thread_local int memo_next = 0;
   for (int i = 0; i < kMemo; ++i) {
     const Memo& m = memo[i];
-    if (m.th && m.N == N && m.Ho == Ho && m.Wo == Wo && m.ipq == items_per_query && m.bpq == bytes_per_query) {
+    if (m.th && m.N == N && m.Ho == Ho && m.Wo == Wo && m.ipq == items_per_query && m.sms == sm_count &&
+        m.bpq == bytes_per_query) {
       *th = m.th; *tw = m.tw;
       return;
     }
@@ -117,14 +118,14 @@ void pick_tile_2d(int N, int Ho, int Wo, size_t bytes_per_query, int items_per_q
     Memo* slot; int* th; int* tw;
     ~Save() { slot->th = *th; slot->tw = *tw; }
   } save{&memo[memo_next], th, tw};
-  memo[memo_next] = Memo{N, Ho, Wo, items_per_query, bytes_per_query, 0, 0};
+  memo[memo_next] = Memo{N, Ho, Wo, items_per_query, sm_count, bytes_per_query, 0, 0};
   memo_next = (memo_next + 1) % kMemo;
   long long max_q = (long long)((kSmemBudget - 64) / bytes_per_query);  // 64: barriers + alignment slack
   const long long cap_items = (6LL * kThreads + items_per_query - 1) / items_per_query;
   if (max_q > cap_items) max_q = cap_items;
   // Several tiles per SM -- but a tile never shrinks below DCNB200_MIN_PASSES full passes of
   // the CTA's threads: on a small batch idle lanes cost more than idle SMs.
-  long long cap_grid = (long long)N * Ho * Wo / (148LL * DCNB200_TILES_PER_SM);
+  long long cap_grid = (long long)N * Ho * Wo / ((long long)sm_count * DCNB200_TILES_PER_SM);
   const long long min_q = ((long long)DCNB200_MIN_PASSES * kThreads + items_per_query - 1) / items_per_query;
   if (cap_grid < min_q) cap_grid = min_q;
   if (max_q > cap_grid) max_q = cap_grid;
@@ -157,11 +158,11 @@ void pick_tile_2d(int N, int Ho, int Wo, size_t bytes_per_query, int items_per_q
 // Queries per CTA of the 1-D tiles (FlashDeformAttn): as many as fit the staging budget, but
 // never so many that the grid drops below a few CTAs per SM; `unit` keeps every tile start
 // 16-byte aligned.
-int pick_tile(long long nq, size_t bytes_per_query, int unit, int items_per_query) {
+int pick_tile(long long nq, size_t bytes_per_query, int unit, int items_per_query, int sm_count) {
   long long t = (long long)((kSmemBudget - 128) / bytes_per_query);
   const long long cap_items = (6LL * kThreads + items_per_query - 1) / items_per_query;
   if (t > cap_items) t = cap_items;
-  const long long cap_grid = nq / (148LL * DCNB200_TILES_PER_SM);
+  const long long cap_grid = nq / ((long long)sm_count * DCNB200_TILES_PER_SM);
   if (cap_grid >= 1 && t > cap_grid) t = cap_grid;
   if (t > 128) t = 128;
   t = (t / unit) * unit;
@@ -194,13 +195,24 @@ int fill_dcn(DcnParams& p, int dtype, int N, int H, int W, int G, int D, int kh,
   p.K = K; p.Ppad = Ppad; p.remove_center = remove_center ? 1 : 0; p.softmax = softmax ? 1 : 0;
   p.scale = offset_scale;
   p.nq = (int)nq;
-  pick_tile_2d(N, Ho, Wo, bpq, G * (backward ? p.tpg_b : p.tpg), &p.th, &p.tw);
-  p.tiles_x = (Wo + p.tw - 1) / p.tw;
-  p.tiles_y = (Ho + p.th - 1) / p.th;
-  if ((long long)N * p.tiles_x * p.tiles_y >= (1LL << 31)) return DCNV4B200_ERR_TOO_LARGE;
   p.div_g = make_div(G);
+  p.th = p.tw = p.tiles_x = p.tiles_y = 0;  // chosen by tile_dcn() once the device is known
+  p.sm_count = 0;
+  return 0;
+}
+
+// Query tile of the validated problem `p` for a device with `sm_count` SMs (arguments are checked
+// before the device is touched, so this runs as a second step).
+int tile_dcn(DcnParams& p, int dtype, bool backward, int sm_count) {
+  if (sm_count < 1) sm_count = 1;
+  const size_t bpq = 2 * (size_t)p.Ppad * elem_size(dtype) + (backward ? (size_t)p.Ppad * 4 : 0) +
+                     (p.softmax ? (size_t)p.G * 8 : 0);
+  pick_tile_2d(p.N, p.Ho, p.Wo, bpq, p.G * (backward ? p.tpg_b : p.tpg), sm_count, &p.th, &p.tw);
+  p.tiles_x = (p.Wo + p.tw - 1) / p.tw;
+  p.tiles_y = (p.Ho + p.th - 1) / p.th;
+  if ((long long)p.N * p.tiles_x * p.tiles_y >= (1LL << 31)) return DCNV4B200_ERR_TOO_LARGE;
   p.div_tw = make_div(p.tw);
-  p.sm_count = 0;  // filled in by device_state() just before a launch
+  p.sm_count = sm_count;
   return 0;
 }
 
@@ -222,10 +234,22 @@ int fill_fda(FdaParams& p, int dtype, int B, int Len_in, int G, int D, int L, in
   if (bpq * unit + 128 > (size_t)kSmemBudget) return DCNV4B200_ERR_UNSUPPORTED;
   p.B = B; p.Len_in = Len_in; p.G = G; p.D = D; p.C = G * D; p.L = L; p.Len_q = Len_q; p.K = K; p.LK = L * K;
   p.nq = (int)nq;
-  p.tile = pick_tile(nq, bpq, unit, G * (backward ? p.tpg_b : p.tpg));
-  while ((size_t)p.tile * bpq + 128 > (size_t)kSmemBudget && p.tile > unit) p.tile -= unit;
+  p.tile = unit;  // chosen by tile_fda() once the device is known
   p.div_g = make_div(G);
   p.sm_count = 0;
+  return 0;
+}
+
+int tile_fda(FdaParams& p, int dtype, bool backward, int sm_count) {
+  if (sm_count < 1) sm_count = 1;
+  const int es = elem_size(dtype);
+  const size_t row_bytes = (size_t)p.G * 3 * p.L * p.K * es;
+  int unit = 1;
+  while ((row_bytes * unit) % 16 != 0) unit *= 2;
+  const size_t bpq = 2 * row_bytes + (backward ? (size_t)p.G * 3 * p.L * p.K * 4 : 0) + (size_t)p.G * 8;
+  p.tile = pick_tile(p.nq, bpq, unit, p.G * (backward ? p.tpg_b : p.tpg), sm_count);
+  while ((size_t)p.tile * bpq + 128 > (size_t)kSmemBudget && p.tile > unit) p.tile -= unit;
+  p.sm_count = sm_count;
   return 0;
 }
 
@@ -275,7 +299,9 @@ int dcnv4b200_fwd(const void* value, const void* offset_mask, void* out, int dty
                         padded_offset_dim, softmax, false, aligned32(value) && aligned32(out)))
     return rc;
   int* status = nullptr;
-  if (int rc = status_ptr(&status, &p.sm_count)) return rc;
+  int sms = 1;
+  if (int rc = status_ptr(&status, &sms)) return rc;
+  if (int rc = tile_dcn(p, dtype, false, sms)) return rc;
   return (int)launch_dcnv4_fwd(dtype, value, offset_mask, out, p, status, static_cast<cudaStream_t>(stream));
 }
 
@@ -299,7 +325,9 @@ int dcnv4b200_bwd(const void* value, const void* offset_mask, const void* grad_o
   const size_t need = dcnv4b200_bwd_workspace_bytes(dtype, N, H, W, G, D);
   if (need && (!workspace || workspace_bytes < need)) return DCNV4B200_ERR_WORKSPACE;
   int* status = nullptr;
-  if (int rc = status_ptr(&status, &p.sm_count)) return rc;
+  int sms = 1;
+  if (int rc = status_ptr(&status, &sms)) return rc;
+  if (int rc = tile_dcn(p, dtype, true, sms)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t n = (size_t)N * H * W * G * D;
   float* acc = need ? static_cast<float*>(workspace) : static_cast<float*>(grad_value);
@@ -307,7 +335,7 @@ int dcnv4b200_bwd(const void* value, const void* offset_mask, const void* grad_o
   if (e != cudaSuccess) return (int)e;
   e = launch_dcnv4_bwd(dtype, value, offset_mask, grad_out, acc, grad_offset_mask, p, status, s);
   if (e != cudaSuccess) return (int)e;
-  if (need) e = launch_convert_f32(dtype, acc, grad_value, n, s);
+  if (need) e = launch_convert_f32(dtype, acc, grad_value, n, sms, s);
   return (int)e;
 }
 
@@ -320,7 +348,9 @@ int fdab200_fwd(const void* value, const int64_t* spatial_shapes, const int64_t*
   if (int rc = fill_fda(p, dtype, B, Len_in, G, D, L, Len_q, K, false, aligned32(value) && aligned32(out)))
     return rc;
   int* status = nullptr;
-  if (int rc = status_ptr(&status, &p.sm_count)) return rc;
+  int sms = 1;
+  if (int rc = status_ptr(&status, &sms)) return rc;
+  tile_fda(p, dtype, false, sms);
   return (int)launch_fda_fwd(dtype, value, spatial_shapes, level_start_index, sampling_loc_attn, out, p, status,
                              static_cast<cudaStream_t>(stream));
 }
@@ -346,7 +376,9 @@ int fdab200_bwd(const void* value, const int64_t* spatial_shapes, const int64_t*
   const size_t need = fdab200_bwd_workspace_bytes(dtype, B, Len_in, G, D);
   if (need && (!workspace || workspace_bytes < need)) return DCNV4B200_ERR_WORKSPACE;
   int* status = nullptr;
-  if (int rc = status_ptr(&status, &p.sm_count)) return rc;
+  int sms = 1;
+  if (int rc = status_ptr(&status, &sms)) return rc;
+  tile_fda(p, dtype, true, sms);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t n = (size_t)B * Len_in * G * D;
   float* acc = need ? static_cast<float*>(workspace) : static_cast<float*>(grad_value);
@@ -355,7 +387,7 @@ int fdab200_bwd(const void* value, const int64_t* spatial_shapes, const int64_t*
   e = launch_fda_bwd(dtype, value, spatial_shapes, level_start_index, sampling_loc_attn, grad_out, acc,
                      grad_sampling_loc_attn, p, status, s);
   if (e != cudaSuccess) return (int)e;
-  if (need) e = launch_convert_f32(dtype, acc, grad_value, n, s);
+  if (need) e = launch_convert_f32(dtype, acc, grad_value, n, sms, s);
   return (int)e;
 }
 
@@ -553,7 +585,9 @@ int dcnv4b200_bwd_static_scratch(const void* value, const void* offset_mask, con
   const bool needs_scratch = dtype != DCNV4B200_F32;
   if (needs_scratch && n > kStaticScratchFloats) return DCNV4B200_ERR_SCRATCH_LIMIT;
   int* status = nullptr;
-  if (int rc = status_ptr(&status, &p.sm_count)) return rc;
+  int sms = 1;
+  if (int rc = status_ptr(&status, &sms)) return rc;
+  if (int rc = tile_dcn(p, dtype, true, sms)) return rc;
   float* acc = static_cast<float*>(grad_value);
   if (needs_scratch) {
     if (int rc = static_scratch_ptr(&acc)) return rc;
@@ -564,7 +598,7 @@ int dcnv4b200_bwd_static_scratch(const void* value, const void* offset_mask, con
   if (e != cudaSuccess) return (int)e;
   e = launch_dcnv4_bwd(dtype, value, offset_mask, grad_out, acc, grad_offset_mask, p, status, s);
   if (e != cudaSuccess) return (int)e;
-  if (needs_scratch) e = launch_convert_f32(dtype, acc, grad_value, n, s);
+  if (needs_scratch) e = launch_convert_f32(dtype, acc, grad_value, n, sms, s);
   return (int)e;
 }
 

@@ -27,12 +27,13 @@ __global__ void convert_kernel(const float4* __restrict__ src, T* __restrict__ d
   }
 }
 
-cudaError_t launch_convert_f32(int dtype, const float* src, void* dst, size_t n, cudaStream_t s) {
+cudaError_t launch_convert_f32(int dtype, const float* src, void* dst, size_t n, int sm_count, cudaStream_t s) {
   if (n == 0) return cudaSuccess;
   const size_t n8 = n / 8;
   const int block = 256;
   size_t want = (n8 + block - 1) / block;
-  const int grid = (int)(want < 1 ? 1 : (want > 148 * 16 ? 148 * 16 : want));
+  const size_t cap = (size_t)(sm_count > 0 ? sm_count : 1) * 16;
+  const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
   if (dtype == 1)
     convert_kernel<__half><<<grid, block, 0, s>>>((const float4*)src, (__half*)dst, n8, n);
   else

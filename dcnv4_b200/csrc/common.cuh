@@ -429,7 +429,7 @@ cudaError_t launch_fda_fwd(int dtype, const void* value, const int64_t* shapes, 
 cudaError_t launch_fda_bwd(int dtype, const void* value, const int64_t* shapes, const int64_t* starts,
                            const void* sla, const void* gout, float* gvalue_f32, void* gsla,
                            const FdaParams& p, int* status, cudaStream_t s);
-cudaError_t launch_convert_f32(int dtype, const float* src, void* dst, size_t n, cudaStream_t s);
+cudaError_t launch_convert_f32(int dtype, const float* src, void* dst, size_t n, int sm_count, cudaStream_t s);
 cudaError_t launch_dcnv4_corners(int dtype, const void* om, int32_t* corners, const DcnParams& p, cudaStream_t s);
 cudaError_t launch_fda_corners(int dtype, const int64_t* shapes, const void* sla, int32_t* corners,
                                const FdaParams& p, cudaStream_t s);

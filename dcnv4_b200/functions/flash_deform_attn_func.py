@@ -14,7 +14,13 @@ from .. import ops
 
 
 class FlashDeformAttnFunction(Function):
+    # The reference decorates forward with autocast(fp16) (flash_deform_attn_func.py:71).  Autocast
+    # only re-types the inputs of PyTorch operators that have an autocast rule; neither the
+    # reference's extension call nor this library's has one, so the operator runs in the dtype of
+    # the tensors it is given, with or without the decorator.  It is kept so that any PyTorch
+    # operator a subclass adds to forward sees the same autocast state as in the reference.
     @staticmethod
+    @torch.autocast("cuda", enabled=True, dtype=torch.float16)
     def forward(ctx, value, value_spatial_shapes, value_level_start_index, sampling_loc_attn,
                 im2col_step, K=8):
         ctx.im2col_step = im2col_step

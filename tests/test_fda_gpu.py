@@ -182,3 +182,39 @@ def test_level_outside_the_value_tensor_is_ignored_and_reported():
     bad_starts[0] = -3
     ops.flash_deform_attn_forward(t["value"], t["spatial_shapes"], bad_starts, t["sampling_loc_attn"], 64, K)
     assert ops.device_status() == 2
+
+
+def test_module_equals_its_parts_around_the_oracle_with_fp16_rounded_locations():
+    """FlashDeformAttn in fp32 = value_proj / sampling_offsets / attention_weights Linears, sampling
+    locations rounded to fp16 as the reference module does (DCNv4_op/DCNv4/modules/flash_deform_attn.py:
+    132-133), the operator, output_proj.  Without that rounding the result differs by more than the tolerance,
+    which the last assertion shows."""
+    import dcnv4_b200
+    torch.manual_seed(5)
+    levels = ((20, 30), (10, 15), (5, 8), (3, 4))
+    mod = dcnv4_b200.FlashDeformAttn(d_model=256, n_levels=4, n_heads=8, n_points=4).to(DEV)
+    with torch.no_grad():
+        mod.sampling_offsets.weight.normal_(0, 0.05)
+        mod.attention_weights.weight.normal_(0, 0.05)
+    shapes, starts, Len = oin.level_tensors(levels)
+    shapes, starts = shapes.to(DEV), starts.to(DEV)
+    q = torch.randn(2, 40, 256, device=DEV)
+    ref_pts = torch.rand(2, 40, 4, 2, device=DEV)
+    feat = torch.randn(2, Len, 256, device=DEV)
+    with torch.no_grad():
+        y = mod(q, ref_pts, feat, shapes, starts)
+        value = mod.value_proj(feat).view(2, Len, 8, 32)
+        off = mod.sampling_offsets(q).view(2, 40, 8, 4, 4, 2)
+        logits = mod.attention_weights(q).view(2, 40, 8, 16)
+        norm = torch.stack([shapes[..., 1], shapes[..., 0]], -1)
+        loc = (ref_pts[:, :, None, :, None, :] + off / norm[None, None, None, :, None, :]).flatten(-3)
+
+        def through_oracle(locations):
+            sla = torch.cat([locations, logits], -1)
+            core = cref.fda_forward(value.cpu(), shapes.cpu(), starts.cpu(), sla.cpu(), 4)
+            return mod.output_proj(core.to(DEV).float())
+
+        ref = through_oracle(loc.half().float())
+        unrounded = through_oracle(loc)
+    close(y, ref, dict(rtol=1e-3, atol=1e-4), "module vs parts with fp16-rounded locations")
+    assert float((unrounded - ref).abs().max()) > 1e-3
