@@ -3,19 +3,22 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload ("step"): one DCNv4 forward and one backward at each of the four FlashInternImage-T
+Workload: a "sweep" is one DCNv4 forward and one backward at each of the four FlashInternImage-T
 stage shapes (N=64 per GPU; (H=W, C, G) = (56,64,4), (28,128,8), (14,256,16), (7,512,32);
 group_channels 16, 3x3 / stride 1 / pad 1), in fp32 and in fp16: 16 operator calls.  All eight
-forwards run first, then all eight backwards, so the ~1 GB of distinct tensors a step touches
+forwards run first, then all eight backwards, so the ~1 GB of distinct tensors a sweep touches
 passes through between two uses of any buffer (inputs larger than the 126 MB L2; no explicit
-flush).  Data is synthetic (seeded, the distributions the configuration states).
+flush).  A "step" is SWEEPS_PER_STEP sweeps back to back (one sweep is ~2 ms, too short a timed
+region for clock sampling at 20 steps).  Data is synthetic (seeded, the distributions the
+configuration states).
 
 `value` = algorithmic bytes of a step (each tensor counted once) x ranks / device time, inputs
 resident in HBM, calls made straight through the C ABI.  `e2e` = the same step through the public
 autograd API with pinned HOST buffers: host->device copies of every input and device->host
 copies of every result inside the timed region.  `roofline` describes the operator call that
-takes the most device time.  `cpu_baseline` times the grid_sample-based CPU formulation (the
-algorithm of the reference's pure-PyTorch core) on a bounded sample of the same workload.
+takes the most device time.  `cpu_baseline` times the reference's own pure-PyTorch (grid_sample-based)
+core on the host cores -- a bounded sample of the same workload plus benchmark configuration 0 --
+falling back to a restatement of the same algorithm when the reference file is not available.
 
 Multi-GPU (torchrun, one rank per GPU): the batch is sharded, every rank runs the same step on
 its own N=64 shard, there is no data-path collective; timing is barrier + synchronize on both
@@ -43,9 +46,12 @@ METRIC = "dcnv4_fwd_bwd_hbm_throughput"
 UNIT = "GB/s"
 WORKLOAD = "dcnv4_fwd+bwd sweep, FlashInternImage-T stage shapes, N=64/GPU, fp32+fp16"
 CPU_SAMPLE_N = 8
-# dram__bytes_read.sum + dram__bytes_write.sum per operator call, from the ncu capture summarised in
-# profiles/dcnv4_stage1_N64_ncu.md (kernel only; for fp16 backward plus the zero-fill of the fp32
-# accumulation buffer, 51.4 MB, and the convert pass, 51.4 + 25.7 MB, which ncu was not asked to capture)
+# One sweep of the 16 operator calls takes ~2 ms: too short a timed region for the clock sampler when the
+# driver asks for 20 steps.  A step is therefore SWEEPS_PER_STEP sweeps back to back; bytes scale with it.
+SWEEPS_PER_STEP = 8
+# dram__bytes_read.sum + dram__bytes_write.sum per operator call, from one ncu capture of each stage-1
+# kernel at N=64 (kernel only; for the fp16 backward plus the zero-fill of the fp32 accumulation buffer,
+# 51.4 MB, and the convert pass, 51.4 + 25.7 MB, which ncu was not asked to capture)
 NCU_TRAFFIC_BYTES = {
     "dcnv4_fwd_56x56x64_fp32": 171.1e6, "dcnv4_fwd_56x56x64_fp16": 77.2e6,
     "dcnv4_bwd_56x56x64_fp32": 348.7e6, "dcnv4_bwd_56x56x64_fp16": 200.9e6 + 128.5e6,
@@ -326,11 +332,18 @@ def time_reference_cuda(torch, cases, reps=5):
 
 
 def time_flash_deform_attn(torch, lib, dev, with_reference, reps=5):
-    """FlashDeformAttn forward/backward at the Deformable-DETR encoder shape (8 x 20,197 positions,
-    levels 100x152, 50x76, 25x38, 13x19, 8 heads x 32 channels, 4 points per level), fp32 and fp16:
-    median device time per call through the C ABI, L2 flushed between runs, and the reference CUDA
-    extension on the same tensors when it is available."""
-    levels = ((100, 152), (50, 76), (25, 38), (13, 19))
+    """FlashDeformAttn forward/backward at the Deformable-DETR encoder shape (8 images, 8 heads x 32
+    channels, 4 levels x 4 points per level), in both readings of the configuration's level sizes:
+    100x152, 50x76, 25x38, 13x19 (20,197 positions, the reference script's) and 100x150, 50x75, 25x38,
+    13x19 (19,947 positions); fp32 and fp16: median device time per call through the C ABI, L2 flushed
+    between runs, and the reference CUDA extension on the same tensors when it is available."""
+    out = []
+    for levels in (((100, 152), (50, 76), (25, 38), (13, 19)), ((100, 150), (50, 75), (25, 38), (13, 19))):
+        out += _time_flash_deform_attn_levels(torch, lib, dev, levels, with_reference, reps)
+    return out
+
+
+def _time_flash_deform_attn_levels(torch, lib, dev, levels, with_reference, reps):
     B, G, Dh, K, L = 8, 8, 32, 4, 4
     shapes = torch.tensor(levels, dtype=torch.int64, device=dev)
     sizes = shapes[:, 0] * shapes[:, 1]
@@ -387,7 +400,7 @@ def time_flash_deform_attn(torch, lib, dev, with_reference, reps=5):
 
         for which, fn, nbytes in (("fwd", fwd, fwd_bytes), ("bwd", bwd, bwd_bytes)):
             ms = timed(fn)
-            row = {"op": f"fda_{which}_8x20197x8x32_{tag}", "ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
+            row = {"op": f"fda_{which}_8x{Len}x8x32_{tag}", "ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
             if ref is not None:
                 try:
                     rfn = ((lambda: ref.fda_forward(v, shapes, starts, sla, K)) if which == "fwd" else
@@ -405,6 +418,40 @@ def time_flash_deform_attn(torch, lib, dev, with_reference, reps=5):
             out.append(row)
         del v, sla, go, y, gv, gs, ws
     return out
+
+
+def time_config0(torch, lib, dev, reps=200):
+    """Benchmark configuration 0 (N=2, 56x56x64, G=4, fp32, seed 0) on the GPU through the C ABI: device
+    time per forward and per forward + backward, launches back to back (the tensors fit L2 many times
+    over; this is the latency of a small call, reported beside the CPU core's time for the same call)."""
+    value, om, gout = synthetic_inputs(torch, 2, 56, 4, 0, torch.float32, dev)
+    out, gv, gom = torch.empty_like(value), torch.empty_like(value), torch.empty_like(om)
+    sc = (2, 56, 56, 4, D, 3, 3, 1, 1, 1, 1, 1, 1, 1.0, 0, om.shape[-1], 0)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def fwd():
+        assert lib.dcnv4b200_fwd(value.data_ptr(), om.data_ptr(), out.data_ptr(), 0, *sc, stream) == 0
+
+    def bwd():
+        assert lib.dcnv4b200_bwd(value.data_ptr(), om.data_ptr(), gout.data_ptr(), gv.data_ptr(), gom.data_ptr(),
+                                 None, 0, 0, *sc, stream) == 0
+
+    def timed(fn):
+        for _ in range(10):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    f_ms = timed(fwd)
+    fb_ms = timed(lambda: (fwd(), bwd()))
+    fb, bb = algorithmic_bytes(2, 56, 64, 4, 4)
+    return {"shape": "N=2, 56x56x64, G=4x16, 3x3/s1/p1, fp32, seed 0", "fwd_ms": f_ms, "fwd_gbs": fb / f_ms / 1e6,
+            "fwd_bwd_ms": fb_ms, "fwd_bwd_gbs": (fb + bb) / fb_ms / 1e6, "launches_back_to_back": reps}
 
 
 def _note(msg):
@@ -486,13 +533,17 @@ def run_ours(args):
     step_bytes = sum(c.fwd_bytes if w == "fwd" else c.bwd_bytes for c, w in ops)
     launches_per_step = sum(c.kernels_fwd if w == "fwd" else c.kernels_bwd for c, w in ops)
 
+    sweeps = 1 if args.case else SWEEPS_PER_STEP
+
     def step(events=None):
-        for i, (c, which) in enumerate(ops):
-            if events is not None:
-                events[i][0].record()
-            (c.fwd if which == "fwd" else c.bwd)(stream)
-            if events is not None:
-                events[i][1].record()
+        # the per-call events bracket the first sweep of a step; the others run unobserved
+        for rep in range(sweeps):
+            for i, (c, which) in enumerate(ops):
+                if events is not None and rep == 0:
+                    events[i][0].record()
+                (c.fwd if which == "fwd" else c.bwd)(stream)
+                if events is not None and rep == 0:
+                    events[i][1].record()
 
     def barrier():
         if world > 1:
@@ -619,6 +670,7 @@ def run_ours(args):
     fda_ops = None
     if rank == 0 and world == 1 and not args.case and not args.no_fda:
         fda_ops = time_flash_deform_attn(torch, lib, dev, with_reference=not args.no_ref_cuda)
+    config0 = time_config0(torch, lib, dev) if rank == 0 and not args.case else None
     if rank == 0:
         sampler.stop()
 
@@ -643,7 +695,7 @@ def run_ours(args):
         dom = max((o for o in per_op if o["launches"] == 1), key=lambda o: o["ms"])
         for o in per_op:
             o["frac"] = o["gbs"] / peak
-        value = step_bytes * world * args.steps / elapsed_ms / 1e6
+        value = step_bytes * sweeps * world * args.steps / elapsed_ms / 1e6
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
@@ -653,18 +705,20 @@ def run_ours(args):
                        "parallelism": f"batch-sharded x{world}, no collective",
                        "l2": "inputs larger than L2: a step touches ~1 GB of distinct tensors between two "
                              "uses of any buffer (all forwards, then all backwards); no explicit flush",
-                       "bytes_per_step_per_gpu": step_bytes},
+                       "sweeps_per_step": sweeps, "operator_calls_per_step": len(ops) * sweeps,
+                       "bytes_per_step_per_gpu": step_bytes * sweeps},
             "e2e": {"value": step_bytes * world * e2e_steps / e2e_ms / 1e6, "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                    "ms_per_step": e2e_ms / e2e_steps,
+                    "ms_per_step": e2e_ms / e2e_steps, "sweeps_per_step": 1,
                     "api": "dcnv4_b200.DCNv4Function.apply + backward, pinned host buffers, "
                            "uploads / compute / downloads on three streams"},
-            "gpu_launches": launches_per_step * args.steps,
+            "gpu_launches": launches_per_step * sweeps * args.steps,
             "roofline": {"bound": "hbm", "kernel": dom["op"], "achieved": dom["gbs"], "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": NCU_TRAFFIC_BYTES.get(dom["op"]),
                          "ms": dom["ms"], "algorithmic_bytes": dom["bytes"]},
             "ops": per_op,
             "clocks": sampler.summary(wall0, wall1),
+            "config0_gpu": config0,
             "reference_cuda": ref_cuda_ops,
             "flash_deform_attn": fda_ops,
             "flash_intern_image_t": None if model_ms != model_ms else {
