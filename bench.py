@@ -749,8 +749,11 @@ def run_ours(args):
 def run_train_l(args):
     """Optional workload (--workload train_l): FlashInternImage-L training step, random-init weights,
     1024x1024 synthetic images, batch 2 per GPU, bf16 autocast, activation checkpointing as in the
-    released -L config, AdamW, DDP gradient all-reduce over NCCL when launched with torchrun.
-    Prints one JSON line with images/s (whole job, max step time over ranks)."""
+    released -L config, AdamW, DDP gradient all-reduce over NCCL when launched with torchrun, with the
+    16-bit gradient compression hook the reference's trainer registers (classification/main.py:228-235;
+    --grad-compress picks fp16 as there, bf16, fp32 or none).  Prints one JSON line with images/s
+    (whole job, max step time over ranks) and, for N > 1, the step time with the gradient exchange
+    switched off (DDP no_sync), whose difference is what the all-reduce costs after overlap."""
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F
@@ -768,19 +771,26 @@ def run_train_l(args):
     torch.manual_seed(0)
     size, res, batch = args.train_size, args.train_res, 2
     model = flash_intern_image(size, with_cp=True).to(dev).train()
+    hooked = False
     if world > 1:
+        from dcnv4_b200 import ddp_hooks
         model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], broadcast_buffers=False,
                                                           gradient_as_bucket_view=True)
+        hooked = ddp_hooks.register(model, args.grad_compress)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.05)
     g = torch.Generator(device="cpu").manual_seed(100 + rank)
     images = torch.randn(batch, 3, res, res, generator=g).to(dev)
     labels = torch.randint(0, 1000, (batch,), generator=g).to(dev)
 
-    def step():
+    import contextlib
+
+    def step(sync=True):
         opt.zero_grad(set_to_none=True)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            loss = F.cross_entropy(model(images).float(), labels)
-        loss.backward()
+        ctx = contextlib.nullcontext() if (sync or world == 1) else model.no_sync()
+        with ctx:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = F.cross_entropy(model(images).float(), labels)
+            loss.backward()
         opt.step()
         return loss
 
@@ -798,10 +808,24 @@ def run_train_l(args):
         loss = step()
     e1.record()
     barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    nosync_ms = float("nan")
+    if world > 1:   # the same step without the gradient exchange (ranks drift apart: timing only)
+        for _ in range(2):
+            step(sync=False)
+        barrier()
+        n0, n1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0.record()
+        for _ in range(args.steps):
+            step(sync=False)
+        n1.record()
+        barrier()
+        nosync_ms = n0.elapsed_time(n1)
+    t = torch.tensor([e0.elapsed_time(e1), nosync_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = t.item() / args.steps
+    ms = t[0].item() / args.steps
+    nosync_ms = t[1].item() / args.steps
+    n_params = sum(p.numel() for p in model.parameters())
     if rank == 0:
         print(json.dumps({
             "metric": f"flash_intern_image_{size}_train_throughput", "value": batch * world / ms * 1e3, "unit": "img/s",
@@ -810,7 +834,14 @@ def run_train_l(args):
             "data": "synthetic", "loss": float(loss.detach()),
             "config": {"workload": f"FlashInternImage-{size.upper()} training step, {res}x{res}, batch {batch}/GPU, "
                                    "AdamW, activation checkpointing, DDP all-reduce",
-                       "global_batch": batch * world, "parallelism": f"dp{world}"},
+                       "global_batch": batch * world, "parallelism": f"dp{world}",
+                       "grad_compress": args.grad_compress if hooked else "none"},
+            "ddp": None if world == 1 else {
+                "ranks_in_process_group": dist.get_world_size(), "backend": dist.get_backend(),
+                "gradient_bytes_fp32": n_params * 4,
+                "wire_bytes_per_step": n_params * (2 if hooked and args.grad_compress in ("fp16", "bf16") else 4),
+                "ms_per_step_without_gradient_exchange": nosync_ms,
+                "allreduce_share_of_step": max(0.0, (ms - nosync_ms) / ms)},
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30}), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -833,6 +864,8 @@ def main():
     ap.add_argument("--workload", choices=("ops", "train_l"), default="ops",
                     help="ops (default): the DCNv4 operator sweep; train_l: FlashInternImage-L training step")
     ap.add_argument("--train-size", default="l", choices=("t", "s", "b", "l"))
+    ap.add_argument("--grad-compress", default="fp16", choices=("none", "fp32", "fp16", "bf16"),
+                    help="DDP gradient all-reduce wire format of --workload train_l (the reference registers fp16)")
     ap.add_argument("--train-res", type=int, default=1024)
     args = ap.parse_args()
     if args.impl == "reference":
