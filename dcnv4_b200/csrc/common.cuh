@@ -417,6 +417,9 @@ cudaError_t launch_dcnv4_bwd(int dtype, const void* value, const void* om, const
                              float* gvalue_f32, void* gom, const DcnParams& p, int* status, cudaStream_t s);
 // Spatially tiled variants (value tile and, for the backward, the grad_value tile in shared
 // memory; dcnv4_*_tiled.cu).  `*_applies` says whether the configuration is covered.
+bool dcnv4_fwd_tiled_applies(const DcnParams& p);
+cudaError_t launch_dcnv4_fwd_tiled(int dtype, const void* value, const void* om, void* out, const DcnParams& p,
+                                   int* status, cudaStream_t s);
 bool dcnv4_bwd_tiled_applies(const DcnParams& p);
 cudaError_t launch_dcnv4_bwd_tiled(int dtype, const void* value, const void* om, const void* gout,
                                    float* gvalue_f32, void* gom, const DcnParams& p, int* status, cudaStream_t s);

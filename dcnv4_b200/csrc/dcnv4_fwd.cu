@@ -203,6 +203,10 @@ static cudaError_t launch_t(const T* value, const T* om, T* out, const DcnParams
 
 cudaError_t launch_dcnv4_fwd(int dtype, const void* value, const void* om, void* out,
                              const DcnParams& p, int* status, cudaStream_t s) {
+  if (tiled_override() == 1 && dcnv4_fwd_tiled_applies(p)) {
+    const cudaError_t e = launch_dcnv4_fwd_tiled(dtype, value, om, out, p, status, s);
+    if (e != cudaErrorNotSupported) return e;  // no tensor-map support in the driver: other kernel
+  }
   switch (dtype) {
     case 0: return launch_t((const float*)value, (const float*)om, (float*)out, p, status, s);
     case 1: return launch_t((const __half*)value, (const __half*)om, (__half*)out, p, status, s);

@@ -69,7 +69,7 @@ def test_flash_deform_attn_detr_encoder_shape_against_oracle(levels, dtype):
         close(gs[b:b + 1], ref_gs, tol_loc, f"grad_sampling_loc_attn, image {b}")
 
 
-# ------------------------------------------------------------ the opt-in tiled backward kernel
+# ------------------------------------------------------------ the opt-in tiled kernels
 
 def _tiled(on: bool):
     if on:
@@ -91,26 +91,32 @@ TILED_CASES = {
     "pad0": (2, 12, 10, 2, 1.0, 1.0, 0),
     "pad2": (2, 12, 10, 2, 1.0, 1.0, 2),
     "tall_33x17": (1, 33, 17, 1, 0.5, 3.0, 1),
+    "far_offsets_g4": (2, 13, 9, 4, 1.0, 6.0, 1),
+    "ragged_19x23_g8": (2, 19, 23, 8, 1.3, 2.0, 1),
 }
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16], ids=["fp32", "fp16", "bf16"])
 @pytest.mark.parametrize("name", sorted(TILED_CASES))
-def test_tiled_backward_parity(name, dtype):
-    """DCNV4B200_TILED=1 routes 3x3 / stride 1 / 16-channel-group backward calls through the kernel that
-    stages the value tile with a TMA box load and pre-accumulates grad_value in shared memory."""
+def test_tiled_kernels_parity(name, dtype):
+    """DCNV4B200_TILED=1 routes 3x3 / stride 1 / 16-channel-group calls through the kernels that stage the
+    value tile with TMA box loads: the backward also pre-accumulates grad_value in shared memory, the
+    forward (group counts that are multiples of four) gathers every corner from the staged box."""
     from dcnv4_b200 import ops
     N, H, W, G, scale, ostd, pad = TILED_CASES[name]
     t = oin.dcnv4_inputs(N, H, W, G, 16, ph=pad, pw=pad, seed=N * 100 + H, offset_std=ostd, dtype=dtype, device=DEV)
     a = (3, 3, 1, 1, pad, pad, 1, 1, G, 16, scale)
     v, om, go = (t[k].float().cpu() for k in ("value", "offset_mask", "grad_out"))
+    ref_out = cref.dcnv4_forward(v, om, *a, 0)
     ref_gv, ref_gom = cref.dcnv4_backward(v, om, go, *a, 0)
     try:
         _tiled(True)
+        out = ops.dcnv4_forward(t["value"], t["offset_mask"], *a, 256, 0)
         gv, gom = ops.dcnv4_backward(t["value"], t["offset_mask"], *a, 256, t["grad_out"], 0)
         torch.cuda.synchronize()
     finally:
         _tiled(False)
+    close(out, ref_out, FWD_TOL[dtype], "forward")
     close(gv, ref_gv, BWD_TOL[dtype], "grad_value")
     close(gom, ref_gom, BWD_TOL[dtype], "grad_offset_mask")
     used = 27 * G
@@ -123,19 +129,31 @@ def test_tiled_backward_parity(name, dtype):
     assert ops.device_status() == 0
 
 
-def test_tiled_backward_full_size_stage1():
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["fp32", "fp16"])
+def test_tiled_kernels_full_size_stage1(dtype):
     from dcnv4_b200 import ops
     N, HW, G = 64, 56, 4
-    t = oin.dcnv4_inputs(N, HW, HW, G, 16, seed=77, dtype=torch.float32, device=DEV)
+    t = oin.dcnv4_inputs(N, HW, HW, G, 16, seed=77, dtype=dtype, device=DEV)
     a = (3, 3, 1, 1, 1, 1, 1, 1, G, 16, 1.0)
     try:
         _tiled(True)
+        out = ops.dcnv4_forward(t["value"], t["offset_mask"], *a, 256, 0)
         gv, gom = ops.dcnv4_backward(t["value"], t["offset_mask"], *a, 256, t["grad_out"], 0)
         torch.cuda.synchronize()
     finally:
         _tiled(False)
+    # identity sampling through the staged box: zero offsets, one-hot centre mask
+    om1 = torch.zeros_like(t["offset_mask"])
+    om1[..., : G * 27].view(N, HW, HW, G, 27)[..., 18 + 4] = 1.0
+    try:
+        _tiled(True)
+        same = ops.dcnv4_forward(t["value"], om1, *a, 256, 0)
+    finally:
+        _tiled(False)
+    assert torch.equal(same, t["value"]), "identity sampling must reproduce the input bit for bit"
     for b in (0, N - 1):
         v, om, go = (t[k][b:b + 1].float().cpu() for k in ("value", "offset_mask", "grad_out"))
+        close(out[b:b + 1], cref.dcnv4_forward(v, om, *a, 0), FWD_TOL[dtype], f"forward, image {b}")
         ref_gv, ref_gom = cref.dcnv4_backward(v, om, go, *a, 0)
-        close(gv[b:b + 1], ref_gv, BWD_TOL[torch.float32], f"grad_value, image {b}")
-        close(gom[b:b + 1], ref_gom, BWD_TOL[torch.float32], f"grad_offset_mask, image {b}")
+        close(gv[b:b + 1], ref_gv, BWD_TOL[dtype], f"grad_value, image {b}")
+        close(gom[b:b + 1], ref_gom, BWD_TOL[dtype], f"grad_offset_mask, image {b}")
