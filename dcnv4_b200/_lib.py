@@ -36,6 +36,7 @@ _SIGNATURES = {
     "fdab200_fwd_corners": (_i, [_p, _p, _p] + [_i] * 6 + [_p]),
     "dcnv4b200_layernorm_fwd": (_i, [_p, _p, _p, _p, _i, _i, C.c_longlong, _i, _f, _p]),
     "dcnv4b200_layernorm_act_fwd": (_i, [_p, _p, _p, _p, _i, _i, C.c_longlong, _i, _f, _i, _p]),
+    "dcnv4b200_center_scale_blend_fwd": (_i, [_p, _p, _p, _p, _p, _i, _i, C.c_longlong, _i, _i, _p]),
     "dcnv4b200_linear_fwd": (_i, [_p, _p, _p, _p, _p, _i, C.c_longlong, _i, _i, _i, _p]),
     "dcnv4b200_bias_act_fwd": (_i, [_p, _p, _p, _i, C.c_longlong, _i, _i, _p]),
     "dcnv4b200_linear_pair_fwd": (_i, [_p, _p, _p, _p, _i, _p, _i, _i, C.c_longlong, _i, _p]),

@@ -434,6 +434,23 @@ int dcnv4b200_layernorm_act_fwd(const void* x, const void* gamma, const void* be
                                    static_cast<cudaStream_t>(stream));
 }
 
+int dcnv4b200_center_scale_blend_fwd(const void* x, const void* x_proj, const void* weight, const void* bias,
+                                     void* out, int dtype, int param_dtype, long long rows, int G, int D,
+                                     void* stream) {
+  if (!x || !x_proj || !weight || !bias || !out) return DCNV4B200_ERR_NULL;
+  if (!dtype_ok(dtype) || (param_dtype != DCNV4B200_F32 && param_dtype != dtype)) return DCNV4B200_ERR_DTYPE;
+  if (rows < 0 || G <= 0 || D <= 0) return DCNV4B200_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(x_proj) || !aligned16(out) || !aligned16(weight)) return DCNV4B200_ERR_ALIGN;
+  if ((D * elem_size(dtype)) % 16 != 0) return DCNV4B200_ERR_CHANNELS;
+  if ((long long)G * D > center_scale_max_channels(dtype) || G > center_scale_max_groups()) return DCNV4B200_ERR_UNSUPPORTED;
+  if (rows == 0) return 0;
+  int* status = nullptr;
+  int sms = 1;
+  if (int rc = status_ptr(&status, &sms)) return rc;
+  return (int)launch_center_scale_blend(dtype, param_dtype, x, x_proj, weight, bias, out, rows, G, D, sms,
+                                        static_cast<cudaStream_t>(stream));
+}
+
 int dcnv4b200_linear_fwd(const void* x, const void* weight, const void* bias, const void* residual, void* y,
                          int dtype, long long M, int N, int K, int activation, void* stream) {
   if (!x || !weight || !y) return DCNV4B200_ERR_NULL;

@@ -472,6 +472,13 @@ cudaError_t launch_layernorm_fwd(int dtype, int param_dtype, const void* x, cons
                                  void* y, long long rows, int C, float eps, int act, int sm_count, cudaStream_t s);
 int layernorm_max_channels(int dtype);
 
+// out = x*(1 - s) + x_proj*s with s = sigmoid(x . weight^T + bias) per row and group (center_scale.cu).
+cudaError_t launch_center_scale_blend(int dtype, int param_dtype, const void* x, const void* xp, const void* w,
+                                      const void* b, void* out, long long rows, int G, int D, int sm_count,
+                                      cudaStream_t s);
+int center_scale_max_channels(int dtype);
+int center_scale_max_groups();
+
 // y = epilogue(x . W^T + bias) on the tensor cores (linear.cu); dtype 1 fp16 / 2 bf16.
 cudaError_t launch_linear_fwd(int dtype, const void* x, const void* w, const void* bias, const void* residual,
                               void* y, long long M, int N, int K, int act, int sms, int* status,

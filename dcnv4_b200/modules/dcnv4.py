@@ -90,6 +90,13 @@ class DCNv4(nn.Module):
             if self.output_proj.bias is not None:
                 constant_(self.output_proj.bias.data, 0.)
 
+    def _blend_fusable(self, x, x_proj) -> bool:
+        w = self.center_feature_scale_proj_weight
+        needs_grad = torch.is_grad_enabled() and (x.requires_grad or x_proj.requires_grad or w.requires_grad)
+        return (not needs_grad and not torch.is_autocast_enabled() and x.dtype == x_proj.dtype
+                and self.center_feature_scale_proj_bias.dtype == w.dtype
+                and ops.center_scale_blend_supported(x, w, self.group_channels))
+
     def forward(self, input, shape=None, residual=None, norm=None):
         """input (N, L, C) with L = H*W; `shape` = (H, W) when the map is not square.
         Returns (N, L, C).  Two extensions over the reference signature serve the layer that
@@ -132,7 +139,11 @@ class DCNv4(nn.Module):
             self.pad, self.pad, self.dilation, self.dilation, self.group, self.group_channels,
             self.offset_scale, 256, self.remove_center)
 
-        if self.center_feature_scale:
+        if self.center_feature_scale and self._blend_fusable(x, x_proj):
+            # inference: Linear + sigmoid + repeat + blend in one pass over x and x_proj
+            x = ops.center_scale_blend_forward(x, x_proj.contiguous(), self.center_feature_scale_proj_weight,
+                                               self.center_feature_scale_proj_bias)
+        elif self.center_feature_scale:
             scale = self.center_feature_scale_module(
                 x, self.center_feature_scale_proj_weight, self.center_feature_scale_proj_bias)
             scale = scale[..., None].repeat(1, 1, 1, 1, self.channels // self.group).flatten(-2)

@@ -191,6 +191,37 @@ def layer_norm_forward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor
     return y
 
 
+def center_scale_blend_supported(x: torch.Tensor, weight: torch.Tensor, D: int) -> bool:
+    """True when `center_scale_blend_forward` covers this input (dtype, size, layout)."""
+    if not (x.is_cuda and x.is_contiguous() and x.dtype in _DTYPES and x.numel() > 0):
+        return False
+    C, es = x.shape[-1], x.element_size()
+    G = weight.shape[0]
+    return (C == G * D and (D * es) % 16 == 0 and C <= (1024 if es == 4 else 2048) and G <= 128
+            and weight.is_cuda and weight.is_contiguous() and weight.dtype in (torch.float32, x.dtype)
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def center_scale_blend_forward(x: torch.Tensor, x_proj: torch.Tensor, weight: torch.Tensor,
+                               bias: torch.Tensor) -> torch.Tensor:
+    """`x * (1 - s) + x_proj * s` with `s = sigmoid(x @ weight.T + bias)` repeated over each group's
+    channels: the centre-feature-scale blend of the DCNv4 module in one pass (forward only; no autograd).
+    x, x_proj (..., G*D) contiguous; weight (G, G*D); bias (G)."""
+    for t, n in ((x, "x"), (x_proj, "x_proj"), (weight, "weight"), (bias, "bias")):
+        _check_tensor(t, n)
+    G, C = weight.shape
+    if x.shape != x_proj.shape or x.shape[-1] != C or x.dtype != x_proj.dtype or C % G != 0 \
+            or bias.numel() != G or bias.dtype != weight.dtype:
+        raise RuntimeError("x and x_proj must be (..., G*D) in one dtype, weight (G, G*D), bias (G)")
+    out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().dcnv4b200_center_scale_blend_fwd(x.data_ptr(), x_proj.data_ptr(), weight.data_ptr(),
+                                                         bias.data_ptr(), out.data_ptr(), _code(x), _code(weight),
+                                                         x.numel() // C, G, C // G, _stream(x))
+    _lib.check(rc, "center_scale_blend_forward")
+    return out
+
+
 def layer_norm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """True when `layer_norm_forward` covers this input (dtype, size, layout)."""
     if not (x.is_cuda and x.is_contiguous() and x.dtype in _DTYPES and x.numel() > 0):

@@ -175,6 +175,20 @@ int dcnv4b200_layernorm_act_fwd(const void* x, const void* gamma, const void* be
                                 int param_dtype, long long rows, int C, float eps, int activation, void* stream);
 
 /*
+ * Centre-feature-scale blend of the DCNv4 module, forward, in one pass:
+ *     s[r, g]   = sigmoid(sum_c x[r, c] * weight[g, c] + bias[g])
+ *     out[r, c] = x[r, c] * (1 - s[r, c / D]) + x_proj[r, c] * s[r, c / D]
+ * Replaces the Linear + sigmoid + repeat + blend of DCNv4_op/DCNv4/modules/dcnv4.py:18-26,142-147
+ * (five PyTorch kernels in the reference; none of its CUDA sources covers them).
+ *   x, x_proj, out (rows, G*D) in `dtype`; weight (G, G*D) and bias (G) in `param_dtype`
+ *   (fp32 or the same as dtype).  D*elem must be a multiple of 16 bytes; G*D at most 1024 (fp32) /
+ *   2048 (fp16, bf16) channels and G at most 128, else DCNV4B200_ERR_UNSUPPORTED.
+ */
+int dcnv4b200_center_scale_blend_fwd(const void* x, const void* x_proj, const void* weight, const void* bias,
+                                     void* out, int dtype, int param_dtype, long long rows, int G, int D,
+                                     void* stream);
+
+/*
  * Linear layer with a fused epilogue, inference only, on the tcgen05 tensor cores:
  *     t = x . weight^T + bias            rounded to `dtype` (what nn.Linear would store)
  *     t = GELU(t)                        if activation == DCNV4B200_ACT_GELU (erf form)

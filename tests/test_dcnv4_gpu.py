@@ -311,3 +311,30 @@ def test_argument_errors():
         v = torch.randn(1, 4, 4, 6, device=DEV)
         om = torch.zeros(1, 4, 4, 56, device=DEV)
         ops.dcnv4_forward(v, om, 3, 3, 1, 1, 1, 1, 1, 1, 2, 3, 1.0, 256, 0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["fp32", "fp16", "bf16"])
+@pytest.mark.parametrize("rows,G,D", [(1, 1, 16), (777, 4, 16), (130, 5, 16), (33, 20, 32), (9, 64, 16), (5, 80, 16)])
+def test_center_scale_blend_kernel_matches_the_reference_formulation(rows, G, D, dtype):
+    """x*(1-s) + x_proj*s with s = sigmoid(Linear(x)) repeated over each group's channels
+    (DCNv4_op/DCNv4/modules/dcnv4.py:18-26,142-147), computed in fp32 from the stored values."""
+    import torch.nn.functional as F
+
+    from dcnv4_b200 import ops
+    C = G * D
+    if dtype == torch.float32 and C > 1024:
+        pytest.skip("fp32 rows above 1024 channels are outside the kernel's range")
+    torch.manual_seed(rows + C)
+    x = torch.randn(rows, C, device=DEV).to(dtype)
+    xp = torch.randn(rows, C, device=DEV).to(dtype)
+    for pdt in {torch.float32, dtype}:
+        w = (torch.randn(G, C, device=DEV) / C ** 0.5).to(pdt)
+        b = torch.randn(G, device=DEV).to(pdt)
+        assert ops.center_scale_blend_supported(x, w, D)
+        got = ops.center_scale_blend_forward(x, xp, w, b)
+        s = F.linear(x.float(), w.float(), b.float()).sigmoid()[..., None].repeat(1, 1, D).flatten(-2)
+        ref = x.float() * (1 - s) + xp.float() * s
+        tol = {torch.float32: dict(rtol=1e-5, atol=1e-5), torch.float16: dict(rtol=2e-3, atol=2e-3),
+               torch.bfloat16: dict(rtol=1.6e-2, atol=1.6e-2)}[dtype]
+        torch.testing.assert_close(got.float(), ref, **tol)
+    assert not ops.center_scale_blend_supported(x[:, : C - 8].contiguous(), w, D)
