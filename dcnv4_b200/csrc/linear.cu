@@ -41,7 +41,9 @@
 // evaluated in fp32 on that rounded value and rounded once more.
 //
 // Building with -DDCNB200_LINEAR_PROFILE adds clock64() timers around the phases of each role
-// (CTA 0 only) and an extra entry point that returns them; it is a tuning aid, off by default.
+// (CTA 0 only) and an extra entry point, dcnv4b200_linear_profile, that returns them; it is a tuning
+// aid, off by default, never part of a shipped build and deliberately not declared in
+// include/dcnv4_b200.h: the header describes exactly what the default build exports.
 #include <cuda.h>
 
 #include <mutex>
