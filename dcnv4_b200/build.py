@@ -66,6 +66,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
         raise RuntimeError("nvcc link failed")
+    for obj in objs:          # every source is recompiled on any change: the objects are of no further use
+        os.remove(obj)
     return LIB
 
 
