@@ -376,6 +376,9 @@ FUSED_LINEAR = True  # benchmarks turn this off to time the stock nn.Linear / GE
 # bounds long reductions by L2 bandwidth: measured against cuBLAS + separate element-wise kernels
 # it wins up to K = 1024 and loses at K = 2048 (FlashInternImage-T stage-4 fc2: 45 vs 36 us).
 FUSED_LINEAR_MAX_K = 1024
+# The LayerNorm epilogue needs a whole row in one tile, i.e. one CTA per 128 rows: below this many
+# rows per SM the separate kernels (narrower tiles, more CTAs) are faster.
+LN_FUSION_MIN_ROWS_PER_SM = 64
 
 
 def linear_module_forward(x: torch.Tensor, lin: "torch.nn.Linear", residual: Optional[torch.Tensor] = None,
@@ -394,7 +397,7 @@ def linear_module_forward(x: torch.Tensor, lin: "torch.nn.Linear", residual: Opt
     # tiles for fewer than half of the SMs the separate kernels (narrower tiles, more CTAs) are
     # faster (measured on FlashInternImage-T stage 3: 98 tiles fused wins, 49 tiles it loses).
     if (fused and norm is not None and activation == "none" and _norm_fusable(norm, lin.out_features, x.dtype)
-            and x.numel() // lin.in_features >= 64 * _sm_count(x.device)):
+            and x.numel() // lin.in_features >= LN_FUSION_MIN_ROWS_PER_SM * _sm_count(x.device)):
         return linear_layer_norm_forward(x, lin.weight, lin.bias, residual, norm.weight, norm.bias, norm.eps)
     if fused:
         y = linear_forward(x, lin.weight, lin.bias, residual, activation)
