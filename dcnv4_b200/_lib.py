@@ -40,6 +40,7 @@ _SIGNATURES = {
     "dcnv4b200_linear_fwd": (_i, [_p, _p, _p, _p, _p, _i, C.c_longlong, _i, _i, _i, _p]),
     "dcnv4b200_bias_act_fwd": (_i, [_p, _p, _p, _i, C.c_longlong, _i, _i, _p]),
     "dcnv4b200_linear_pair_fwd": (_i, [_p, _p, _p, _p, _i, _p, _i, _i, C.c_longlong, _i, _p]),
+    "dcnv4b200_fwd_fused_offset": (_i, [_p] * 5 + [_i] * 8 + [_f, _p]),
     "dcnv4b200_linear_ln_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _f, _p, _i, C.c_longlong, _i, _i, _p]),
     "dcnv4b200_device_status": (_i, [C.POINTER(_i)]),
     "dcnv4b200_bwd_static_scratch_max_elements": (_z, []),

@@ -20,7 +20,7 @@ OUT_DIR = os.path.join(HERE, "_C")
 LIB = os.path.join(OUT_DIR, "libdcnv4_b200.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
-SOURCES = ("api.cu", "dcnv4_fwd.cu", "dcnv4_bwd.cu", "dcnv4_bwd_tiled.cu", "dcnv4_fwd_tiled.cu", "fda_fwd.cu", "fda_bwd.cu", "aux.cu", "layernorm.cu",
+SOURCES = ("api.cu", "dcnv4_fwd.cu", "dcnv4_bwd.cu", "dcnv4_bwd_tiled.cu", "dcnv4_fwd_tiled.cu", "dcnv4_fwd_fused.cu", "fda_fwd.cu", "fda_bwd.cu", "aux.cu", "layernorm.cu",
            "linear.cu", "bias_act.cu", "center_scale.cu")
 ARCH = ("-gencode", "arch=compute_100a,code=sm_100a")
 NVCC_FLAGS = ("-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr")

@@ -508,6 +508,28 @@ int dcnv4b200_linear_pair_fwd(const void* x, const void* weight, const void* bia
                                 static_cast<cudaStream_t>(stream), nullptr, nullptr, 0.f, y2, N1);
 }
 
+int dcnv4b200_fwd_fused_offset(const void* value, const void* x, const void* weight, const void* bias, void* out,
+                               int dtype, int N, int H, int W, int G, int D, int K, int weight_rows,
+                               float offset_scale, void* stream) {
+  if (!value || !x || !weight || !out) return DCNV4B200_ERR_NULL;
+  if (dtype != DCNV4B200_F16 && dtype != DCNV4B200_BF16) return DCNV4B200_ERR_DTYPE;
+  if (N < 0 || H <= 0 || W <= 0 || G <= 0 || D <= 0 || K <= 0 || weight_rows <= 0) return DCNV4B200_ERR_SHAPE;
+  if (weight_rows < 27 * G) return DCNV4B200_ERR_PADDED_DIM;
+  if (K % 8 != 0) return DCNV4B200_ERR_CHANNELS;
+  if (!dcnv4_fwd_fused_applies(dtype, G, D, K, weight_rows)) return DCNV4B200_ERR_UNSUPPORTED;
+  // a lane fetches the 16 channels of a group with one 32-byte load
+  if (!aligned32(value) || !aligned32(out) || !aligned16(x) || !aligned16(weight) || ((uintptr_t)bias & 1))
+    return DCNV4B200_ERR_ALIGN;
+  if ((long long)N * H * W >= (1LL << 31) - 128 || (long long)N * H * W * G * D >= (1LL << 31))
+    return DCNV4B200_ERR_TOO_LARGE;
+  if (N == 0) return 0;
+  int* status = nullptr;
+  int sms = 1;
+  if (int rc = status_ptr(&status, &sms)) return rc;
+  return (int)launch_dcnv4_fwd_fused(dtype, value, x, weight, bias, out, N, H, W, G, K, weight_rows, offset_scale,
+                                     sms, status, static_cast<cudaStream_t>(stream));
+}
+
 int dcnv4b200_bias_act_fwd(const void* x, const void* bias, void* y, int dtype, long long rows, int C,
                            int activation, void* stream) {
   if (!x || !bias || !y) return DCNV4B200_ERR_NULL;

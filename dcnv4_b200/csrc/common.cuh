@@ -423,6 +423,13 @@ cudaError_t launch_dcnv4_fwd_tiled(int dtype, const void* value, const void* om,
 bool dcnv4_bwd_tiled_applies(const DcnParams& p);
 cudaError_t launch_dcnv4_bwd_tiled(int dtype, const void* value, const void* om, const void* gout,
                                    float* gvalue_f32, void* gom, const DcnParams& p, int* status, cudaStream_t s);
+// DCNv4 forward that computes its offset/mask rows itself from the layer input and the weights of the
+// module's offset/mask Linear (dcnv4_fwd_fused.cu; 16-bit tensors, 3x3 / stride 1 / pad 1 /
+// dilation 1, D = 16).
+bool dcnv4_fwd_fused_applies(int dtype, int G, int D, int K, int w_rows);
+cudaError_t launch_dcnv4_fwd_fused(int dtype, const void* value, const void* x, const void* w, const void* bias,
+                                   void* out, int N, int H, int W, int G, int K, int w_rows, float scale, int sms,
+                                   int* status, cudaStream_t stream);
 // Kernel choice for configurations both kernels cover: environment variable DCNV4B200_TILED,
 // read at every call; 1 selects the tiled kernel, anything else (-1 unset, 0) the default one.
 // Meant for A/B measurements and for the tests of the tiled kernel.

@@ -97,6 +97,16 @@ class DCNv4(nn.Module):
                 and self.center_feature_scale_proj_bias.dtype == w.dtype
                 and ops.center_scale_blend_supported(x, w, self.group_channels))
 
+    def _offsets_fusable(self, input) -> bool:
+        needs_grad = torch.is_grad_enabled() and (input.requires_grad or self.offset_mask.weight.requires_grad
+                                                  or self.value_proj.weight.requires_grad)
+        return (ops.FUSED_OFFSET_MASK and not needs_grad and not torch.is_autocast_enabled()
+                and not self.without_pointwise and self.dw_kernel_size is None and not self.center_feature_scale
+                and not self.remove_center and self.kernel_size == 3 and self.stride == 1 and self.pad == 1
+                and self.dilation == 1 and self.group_channels == 16 and self.group % 4 == 0
+                and input.is_cuda and input.is_contiguous()
+                and input.dtype in (torch.float16, torch.bfloat16) and self.offset_mask.weight.dtype == input.dtype)
+
     def forward(self, input, shape=None, residual=None, norm=None):
         """input (N, L, C) with L = H*W; `shape` = (H, W) when the map is not square.
         Returns (N, L, C).  Two extensions over the reference signature serve the layer that
@@ -108,6 +118,15 @@ class DCNv4(nn.Module):
             H, W = shape
         else:
             H, W = int(L ** 0.5), int(L ** 0.5)
+
+        if self._offsets_fusable(input):
+            # inference: the offset/mask rows are produced by the sampling kernel itself
+            x = ops.linear_module_forward(input, self.value_proj).reshape(N, H, W, -1)
+            if ops.fused_offset_supported(x, input, self.offset_mask.weight, self.offset_mask.bias, self.group,
+                                          self.group_channels):
+                x = ops.dcnv4_fused_offset_forward(x, input, self.offset_mask.weight, self.offset_mask.bias,
+                                                   self.group, self.group_channels, self.offset_scale)
+                return ops.linear_module_forward(x.view(N, L, -1), self.output_proj, residual, "none", norm)
 
         paired = None
         if not self.without_pointwise and self.dw_kernel_size is None:

@@ -6,6 +6,7 @@ and call the library on the current CUDA stream.
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -326,6 +327,60 @@ def linear_pair_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[to
     return y1, y2
 
 
+def fused_offset_supported(value: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
+                           bias: Optional[torch.Tensor], group: int, group_channels: int) -> bool:
+    """True when `dcnv4_fused_offset_forward` covers these tensors (the kernel is specialised for
+    3x3 / stride 1 / pad 1 / dilation 1, which the caller checks)."""
+    if not (value.is_cuda and value.dtype in (torch.float16, torch.bfloat16) and value.is_contiguous()
+            and value.dim() == 4 and value.numel() > 0 and value.data_ptr() % 32 == 0):
+        return False
+    if not (x.is_cuda and x.dtype == value.dtype and x.is_contiguous() and x.data_ptr() % 16 == 0):
+        return False
+    if not (weight.is_cuda and weight.dtype == value.dtype and weight.is_contiguous() and weight.dim() == 2
+            and weight.data_ptr() % 16 == 0):
+        return False
+    if bias is not None and not (bias.is_cuda and bias.dtype == value.dtype and bias.is_contiguous()
+                                 and bias.numel() == weight.shape[0]):
+        return False
+    N, H, W, C = value.shape
+    rows, K = weight.shape
+    return (group_channels == 16 and C == 16 * group and group % 4 == 0 and group <= 128
+            and K % 8 == 0 and x.shape[-1] == K and x.numel() == N * H * W * K and rows >= 27 * group
+            and value.numel() < 2 ** 31)
+
+
+def dcnv4_fused_offset_forward(value: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
+                               bias: Optional[torch.Tensor], group: int, group_channels: int,
+                               offset_scale: float) -> torch.Tensor:
+    """`dcnv4_forward(value, linear(x, weight, bias), 3, 3, 1, 1, 1, 1, 1, 1, group, group_channels,
+    offset_scale, ...)` in one kernel: the offset/mask rows are computed by the CTA that samples
+    for them and are never stored (forward only; fp16 / bf16).  value (N,H,W,C), x (N,H*W,K) or
+    (N,H,W,K), weight (P,K) with P >= 27*group, bias (P) or None."""
+    for t, name in ((value, "input"), (x, "offset_mask input"), (weight, "weight")):
+        _check_tensor(t, name)
+    if value.dim() != 4:
+        raise RuntimeError("input must be an (N,H,W,C) tensor")
+    N, H, W, C = value.shape
+    if C != group * group_channels:
+        raise RuntimeError(
+            f"Input channels and group times group channels wont match: ({C} vs {group * group_channels}).")
+    rows, K = weight.shape
+    if x.dtype != value.dtype or weight.dtype != value.dtype or x.shape[-1] != K or x.numel() != N * H * W * K:
+        raise RuntimeError("offset_mask input must be (N,H*W,K) and weight (P,K), in the dtype of the input")
+    if bias is not None:
+        _check_tensor(bias, "bias")
+        if bias.dtype != value.dtype or bias.numel() != rows:
+            raise RuntimeError("bias must have one element per weight row, in the dtype of the input")
+    out = torch.empty_like(value)
+    with torch.cuda.device(value.device):
+        rc = _lib.lib().dcnv4b200_fwd_fused_offset(value.data_ptr(), x.data_ptr(), weight.data_ptr(),
+                                                   bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                                                   _code(value), N, H, W, group, group_channels, K, rows,
+                                                   float(offset_scale), _stream(value))
+    _lib.check(rc, "dcnv4_fused_offset_forward")
+    return out
+
+
 class PairedLinear:
     """Inference-time cache of two nn.Linear layers that read the same input, stacked for
     `linear_pair_forward`.  The stacked copy is rebuilt whenever a parameter changed (version
@@ -376,6 +431,10 @@ FUSED_LINEAR = True  # benchmarks turn this off to time the stock nn.Linear / GE
 # bounds long reductions by L2 bandwidth: measured against cuBLAS + separate element-wise kernels
 # it wins up to K = 1024 and loses at K = 2048 (FlashInternImage-T stage-4 fc2: 45 vs 36 us).
 FUSED_LINEAR_MAX_K = 1024
+# DCNv4 module at inference: compute the offset/mask rows inside the sampling kernel
+# (`dcnv4_fused_offset_forward`) instead of storing them from the paired projection.  Environment
+# variable DCNV4B200_FUSED_OFFSET=0/1 overrides the default.
+FUSED_OFFSET_MASK = os.environ.get("DCNV4B200_FUSED_OFFSET", "0") == "1"
 # The LayerNorm epilogue needs a whole row in one tile, i.e. one CTA per 128 rows: below this many
 # rows per SM the separate kernels (narrower tiles, more CTAs) are faster.
 LN_FUSION_MIN_ROWS_PER_SM = 64

@@ -233,6 +233,24 @@ int dcnv4b200_linear_pair_fwd(const void* x, const void* weight, const void* bia
                               int N2, int dtype, long long M, int K, void* stream);
 
 /*
+ * DCNv4 forward that computes the offset/mask rows itself (inference):
+ *     offset_mask = x . weight^T + bias,    out = dcnv4b200_fwd(value, offset_mask, 3x3, stride 1, pad 1,
+ *                                                  dilation 1, no softmax, remove_center 0)
+ * in one kernel.  The rows of 128 consecutive positions are produced on the tensor cores by the CTA
+ * that samples for them, rounded to `dtype` as the Linear would have stored them, and never go to
+ * memory.  In the reference this is `self.offset_mask(input)` followed by `DCNv4Function.apply`
+ * (DCNv4_op/DCNv4/modules/dcnv4.py:121-140) with the (N, H, W, padded 27 G) tensor between them.
+ *   value, out (N, H, W, G*D), 32-byte aligned; x (N*H*W, K) and weight (weight_rows, K) row-major,
+ *   16-byte aligned; bias (weight_rows) or NULL; all fp16 or all bf16.
+ *   D must be 16 and G a multiple of 4 up to 128 (DCNV4B200_ERR_UNSUPPORTED otherwise: the caller
+ *   then runs the two steps separately); K a multiple of 8; weight_rows >= 27 G
+ *   (_ERR_PADDED_DIM), rows beyond 27 G -- the Linear's padding -- are ignored.
+ */
+int dcnv4b200_fwd_fused_offset(const void* value, const void* x, const void* weight, const void* bias, void* out,
+                               int dtype, int N, int H, int W, int G, int D, int K, int weight_rows,
+                               float offset_scale, void* stream);
+
+/*
  * y = act(x + bias) over the last dimension of a channels-last tensor, in one pass:
  *   x, y (rows, C) contiguous in `dtype` (fp16 or bf16; y may alias x), bias (C) in `dtype`,
  *   C a multiple of 8, activation DCNV4B200_ACT_NONE or DCNV4B200_ACT_GELU (erf form, on the

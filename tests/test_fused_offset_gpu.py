@@ -1,0 +1,105 @@
+"""DCNv4 forward that computes its own offset/mask rows on the tensor cores, against the two-step
+sequence it replaces (the module's `offset_mask` Linear, then the sampling kernel;
+DCNv4_op/DCNv4/modules/dcnv4.py:121-140) and against the CPU oracle.
+
+The fused kernel rounds the Linear's result to the storage type before it samples, exactly as the
+separate Linear stores it, and samples with the same arithmetic as the stand-alone kernel: the two
+paths may differ only where the two products accumulate in a different order.  Tolerance: the
+forward tolerance of the 16-bit types (fp16 rtol 1e-2 / atol 1e-3, bf16 rtol 2e-2 / atol 1e-2)."""
+import pytest
+import torch
+
+from tests.util import FWD_TOL, close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+# (N, H, W, G, K): the four FlashInternImage-T stage shapes at a small batch, a batch whose last
+# 128-query tile is ragged and straddles images, K not a multiple of 64, a single query, the widest K.
+SHAPES = [(2, 56, 56, 4, 64), (3, 28, 28, 8, 128), (5, 14, 14, 16, 256), (3, 7, 7, 32, 512), (3, 5, 9, 8, 72),
+          (1, 1, 1, 4, 64), (2, 9, 7, 12, 192), (1, 12, 11, 4, 1024)]
+
+
+def _inputs(N, H, W, G, K, dtype, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    P = (27 * G + 7) // 8 * 8
+    value = torch.randn(N, H, W, 16 * G, generator=g).to(dtype).to(DEV)
+    x = torch.randn(N, H * W, K, generator=g).to(dtype).to(DEV)
+    w = (torch.randn(P, K, generator=g) / K ** 0.5).to(dtype).to(DEV)
+    b = (0.5 * torch.randn(P, generator=g)).to(dtype).to(DEV)
+    return value, x, w, b
+
+
+def _two_step(value, x, w, b, G, scale):
+    from dcnv4_b200 import ops
+    N, H, W, _ = value.shape
+    om = ops.linear_forward(x.reshape(N * H * W, -1), w, b).reshape(N, H, W, -1)
+    return ops.dcnv4_forward(value, om, 3, 3, 1, 1, 1, 1, 1, 1, G, 16, scale, 256, 0), om
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("N,H,W,G,K", SHAPES)
+def test_fused_matches_linear_then_sampling(N, H, W, G, K, dtype):
+    from dcnv4_b200 import ops
+    value, x, w, b = _inputs(N, H, W, G, K, dtype, seed=N * 1000 + H * 10 + G)
+    assert ops.fused_offset_supported(value, x, w, b, G, 16)
+    for bias, scale in ((b, 1.0), (None, 2.0), (b, 0.5)):
+        out = ops.dcnv4_fused_offset_forward(value, x, w, bias, G, 16, scale)
+        ref, _ = _two_step(value, x, w, bias, G, scale)
+        assert out.shape == value.shape and out.dtype == dtype
+        close(out, ref, FWD_TOL[dtype], f"fused vs two-step, scale {scale}")
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("N,H,W,G,K", [(2, 14, 14, 4, 64), (1, 9, 12, 8, 128), (1, 7, 7, 16, 256)])
+def test_fused_matches_oracle(N, H, W, G, K, dtype):
+    """Oracle on the offset/mask rows the separate Linear stores (the fused kernel's rows are the
+    same products rounded the same way)."""
+    from dcnv4_b200 import ops
+    from oracle import cref
+    value, x, w, b = _inputs(N, H, W, G, K, dtype, seed=77 + G)
+    out = ops.dcnv4_fused_offset_forward(value, x, w, b, G, 16, 1.0)
+    _, om = _two_step(value, x, w, b, G, 1.0)
+    want = cref.dcnv4_forward(value.float().cpu(), om.float().cpu(), 3, 3, 1, 1, 1, 1, 1, 1, G, 16, 1.0, 0)
+    close(out, want, FWD_TOL[dtype], "fused vs oracle")
+
+
+def test_fused_rejects_what_it_does_not_cover():
+    from dcnv4_b200 import ops
+    value, x, w, b = _inputs(1, 4, 4, 4, 64, torch.float16, seed=1)
+    # 32 channels per group, a group count that is not a multiple of 4, fp32 tensors
+    assert not ops.fused_offset_supported(value, x, w, b, 2, 32)
+    v6 = torch.randn(1, 4, 4, 96, device=DEV, dtype=torch.float16)
+    w6 = torch.randn(168, 64, device=DEV, dtype=torch.float16)
+    assert not ops.fused_offset_supported(v6, x, w6, None, 6, 16)
+    assert not ops.fused_offset_supported(value.float(), x.float(), w.float(), b.float(), 4, 16)
+    with pytest.raises(ValueError):  # unsupported parameter values, as for the other operators
+        ops.dcnv4_fused_offset_forward(v6, x, w6, None, 6, 16, 1.0)
+    # too few weight rows for 27 columns per group
+    with pytest.raises(RuntimeError):
+        ops.dcnv4_fused_offset_forward(value, x, w[:104].contiguous(), None, 4, 16, 1.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+def test_module_with_fused_offsets_matches_module_without(dtype):
+    from dcnv4_b200 import ops
+    from dcnv4_b200.modules import DCNv4
+    torch.manual_seed(5)
+    m = DCNv4(channels=128, group=8, offset_scale=1.0, dw_kernel_size=None, output_bias=True).to(DEV)
+    with torch.no_grad():
+        m.offset_mask.weight.normal_(0, 0.1)
+        m.offset_mask.bias.normal_(0, 0.3)
+    m = m.to(dtype).eval()
+    x = torch.randn(3, 14 * 14, 128, device=DEV).to(dtype)
+    saved = ops.FUSED_OFFSET_MASK
+    try:
+        with torch.no_grad():
+            ops.FUSED_OFFSET_MASK = True
+            y_fused = m(x)
+            ops.FUSED_OFFSET_MASK = False
+            y_plain = m(x)
+    finally:
+        ops.FUSED_OFFSET_MASK = saved
+    close(y_fused, y_plain, FWD_TOL[dtype], "module, fused offsets vs separate Linear")
+    assert ops.device_status() == 0
