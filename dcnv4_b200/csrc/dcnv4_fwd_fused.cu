@@ -80,7 +80,7 @@ struct FusedParams {
   int k_blocks, m_tiles, chunks;
   int stages;        // ring slots
   int n_cols;        // 27 G: columns of the Linear that carry offsets and masks
-  int bias_floats;   // n_cols rounded up to a multiple of 4
+  int bias_floats;   // staged bias: 28 floats per group (27 + one of padding, for 16-byte loads)
   float scale;
   const void* bias;  // (>= n_cols) or null
   int* status;
@@ -196,13 +196,19 @@ dcnv4_fwd_fused_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     constexpr int kSlots = GC / 4;       // group slots a warp parks per task
     {
       const T* bias = static_cast<const T*>(p.bias);
-      for (int i = wtid; i < p.bias_floats; i += kWorkThreads)
-        s_bias[i] = (bias != nullptr && i < p.n_cols) ? to_f32(bias[i]) : 0.f;
+      for (int i = wtid; i < p.bias_floats; i += kWorkThreads) {
+        const int g = i / 28, c = i - g * 28;
+        s_bias[i] = (bias != nullptr && c < kPts) ? to_f32(bias[g * kPts + c]) : 0.f;
+      }
     }
     work_barrier();
 
     const int HW = p.H * p.W;
     const float Hf = (float)p.H, Wf = (float)p.W;
+    // n / d as umulhi(n, floor(2^32 / d) + 1): never below the quotient and at most one above it for
+    // n < 2^31, which one comparison repairs.
+    const uint32_t mul_hw = (uint32_t)(0x100000000ull / (uint32_t)HW) + 1u;
+    const uint32_t mul_w = (uint32_t)(0x100000000ull / (uint32_t)p.W) + 1u;
     uint32_t it = 0;
     for (long long t = blockIdx.x; t < n_tasks; t += gridDim.x, ++it) {
       const int acc = (int)(it & 1);
@@ -219,12 +225,14 @@ dcnv4_fwd_fused_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           uint32_t v[32];
           tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + gl * kSlot), v);
           tmem_ld_wait();
-          const float* b = s_bias + (ch * GC + gl) * kPts;
+          const float4* b4 = reinterpret_cast<const float4*>(s_bias + (ch * GC + gl) * 28);
           uint32_t o[14];
 #pragma unroll
-          for (int i = 0; i < 13; ++i)
-            o[i] = pack2<T>(__uint_as_float(v[2 * i]) + b[2 * i], __uint_as_float(v[2 * i + 1]) + b[2 * i + 1]);
-          o[13] = pack2<T>(__uint_as_float(v[26]) + b[26], 0.f);
+          for (int i = 0; i < 7; ++i) {  // the 28th value (padding) is parked too and never read
+            const float4 b = b4[i];
+            o[2 * i] = pack2<T>(__uint_as_float(v[4 * i]) + b.x, __uint_as_float(v[4 * i + 1]) + b.y);
+            o[2 * i + 1] = pack2<T>(__uint_as_float(v[4 * i + 2]) + b.z, __uint_as_float(v[4 * i + 3]) + b.w);
+          }
           unsigned char* dst = stage_rows + lane * PITCH + gl * kGroupBytes;  // 8-byte aligned
 #pragma unroll
           for (int i = 0; i < 14; i += 2) *reinterpret_cast<uint2*>(dst + i * 4) = make_uint2(o[i], o[i + 1]);
@@ -241,10 +249,19 @@ dcnv4_fwd_fused_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         const int ql = item / GC, gl = item % GC;
         const int q = mt * kQ + quad * 32 + ql;  // M < 2^31 - 128 (checked by the caller)
         if (q >= (int)p.M) continue;
-        const int b = q / HW;
-        const int r = q - b * HW;
-        const int y = r / p.W, x = r - y * p.W;
-        const T* om = reinterpret_cast<const T*>(stage_rows + ql * PITCH + gl * kGroupBytes);
+        int b = HW == 1 ? q : (int)__umulhi((uint32_t)q, mul_hw);
+        int r = q - b * HW;
+        if (r < 0) { --b; r += HW; }
+        int y = p.W == 1 ? r : (int)__umulhi((uint32_t)r, mul_w);
+        int x = r - y * p.W;
+        if (x < 0) { --y; x += p.W; }
+        // the 27 parked values of this (query, group): seven 8-byte loads
+        uint32_t omw[14];
+        {
+          const uint2* src = reinterpret_cast<const uint2*>(stage_rows + ql * PITCH + gl * kGroupBytes);
+#pragma unroll
+          for (int i = 0; i < 7; ++i) { const uint2 u = src[i]; omw[2 * i] = u.x; omw[2 * i + 1] = u.y; }
+        }
         // 3x3 / stride 1 / pad 1 / dilation 1: first tap at (x - 1, y - 1) before scaling
         const float base_w = dcn_base(x, 1, p.scale);
         const float base_h = dcn_base(y, 1, p.scale);
@@ -258,9 +275,11 @@ dcnv4_fwd_fused_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 #pragma unroll
           for (int j = 0; j < 3; ++j) {
             const int k = i * 3 + j;
-            const float w_im = dcn_coord(base_w, (float)i, to_f32(om[2 * k]), p.scale);
-            const float h_im = dcn_coord(base_h, (float)j, to_f32(om[2 * k + 1]), p.scale);
-            fwd_point<T, 16>(img, p.H, p.W, p.C, Hf, Wf, h_im, w_im, to_f32(om[18 + k]), a16);
+            const float2 off = unpack2<T>(omw[k]);  // (dx, dy) of tap k
+            const float2 mk = unpack2<T>(omw[(18 + k) >> 1]);
+            const float w_im = dcn_coord(base_w, (float)i, off.x, p.scale);
+            const float h_im = dcn_coord(base_h, (float)j, off.y, p.scale);
+            fwd_point<T, 16>(img, p.H, p.W, p.C, Hf, Wf, h_im, w_im, ((18 + k) & 1) ? mk.y : mk.x, a16);
           }
         }
         uint32_t packed[8];
@@ -284,7 +303,7 @@ template <typename T, int GC>
 cudaError_t launch_gc(int dtype, const void* value, const void* x, const void* w, void* out, FusedParams p, int w_rows,
                       int K, int sms, cudaStream_t stream) {
   p.chunks = p.G / GC;
-  p.bias_floats = (p.n_cols + 3) / 4 * 4;
+  p.bias_floats = 28 * p.G;
   p.stages = ring_stages(p.k_blocks);
   const size_t smem = fused_smem<GC>(p.bias_floats, p.stages);
   if (smem > 227 * 1024) return cudaErrorInvalidValue;

@@ -6,11 +6,21 @@ at 9.0, flash_deform_attn_func.py:21-36); this module has no such gate.
 """
 from __future__ import annotations
 
+import warnings
+
 import torch
 from torch.autograd import Function
 from torch.autograd.function import once_differentiable
 
 from .. import ops
+
+
+def _autocast_fp16(fn):
+    # Building the decorator on a host without CUDA (CPU-side tests import this module) makes PyTorch
+    # warn that it disables autocast; there is nothing to run on such a host anyway.
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        return torch.autocast("cuda", enabled=True, dtype=torch.float16)(fn)
 
 
 class FlashDeformAttnFunction(Function):
@@ -20,7 +30,7 @@ class FlashDeformAttnFunction(Function):
     # the tensors it is given, with or without the decorator.  It is kept so that any PyTorch
     # operator a subclass adds to forward sees the same autocast state as in the reference.
     @staticmethod
-    @torch.autocast("cuda", enabled=True, dtype=torch.float16)
+    @_autocast_fp16
     def forward(ctx, value, value_spatial_shapes, value_level_start_index, sampling_loc_attn,
                 im2col_step, K=8):
         ctx.im2col_step = im2col_step

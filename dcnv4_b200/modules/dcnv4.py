@@ -100,7 +100,8 @@ class DCNv4(nn.Module):
     def _offsets_fusable(self, input) -> bool:
         needs_grad = torch.is_grad_enabled() and (input.requires_grad or self.offset_mask.weight.requires_grad
                                                   or self.value_proj.weight.requires_grad)
-        return (ops.FUSED_OFFSET_MASK and not needs_grad and not torch.is_autocast_enabled()
+        return (ops.fused_offset_pays(input.numel() // input.shape[-1], self.channels, input.device)
+                and not needs_grad and not torch.is_autocast_enabled()
                 and not self.without_pointwise and self.dw_kernel_size is None and not self.center_feature_scale
                 and not self.remove_center and self.kernel_size == 3 and self.stride == 1 and self.pad == 1
                 and self.dilation == 1 and self.group_channels == 16 and self.group % 4 == 0

@@ -432,9 +432,28 @@ FUSED_LINEAR = True  # benchmarks turn this off to time the stock nn.Linear / GE
 # it wins up to K = 1024 and loses at K = 2048 (FlashInternImage-T stage-4 fc2: 45 vs 36 us).
 FUSED_LINEAR_MAX_K = 1024
 # DCNv4 module at inference: compute the offset/mask rows inside the sampling kernel
-# (`dcnv4_fused_offset_forward`) instead of storing them from the paired projection.  Environment
-# variable DCNV4B200_FUSED_OFFSET=0/1 overrides the default.
-FUSED_OFFSET_MASK = os.environ.get("DCNV4B200_FUSED_OFFSET", "0") == "1"
+# (`dcnv4_fused_offset_forward`) instead of storing them from the paired projection.  Measured on a
+# B200, fp16, value projection + fused kernel against paired projection + sampling kernel, us:
+#   batch 256: 56x56x64 330 / 338, 28x28x128 175 / 193, 14x14x256 100 / 114, 7x7x512 68 / 67;
+#   batch 32:  60 / 56, 40 / 42, 33 / 37, 30 / 37.
+# It pays from 128 channels upward at any batch and at 64 channels only for large batches, hence the
+# two thresholds.  Environment variable DCNV4B200_FUSED_OFFSET=0 turns it off, =1 forces it wherever
+# the kernel applies (tests).
+_FUSED_OFFSET_ENV = os.environ.get("DCNV4B200_FUSED_OFFSET", "")
+FUSED_OFFSET_MASK = _FUSED_OFFSET_ENV != "0"
+FUSED_OFFSET_MIN_CHANNELS = 128
+FUSED_OFFSET_MIN_ROWS_NARROW = 4096  # rows per SM below which 64-channel layers keep the two-step path
+
+
+def fused_offset_pays(rows: int, channels: int, device) -> bool:
+    """Whether the module should take the fused kernel for a layer of this size (see above)."""
+    if not FUSED_OFFSET_MASK:
+        return False
+    if _FUSED_OFFSET_ENV == "1" or channels >= FUSED_OFFSET_MIN_CHANNELS:
+        return True
+    return rows >= FUSED_OFFSET_MIN_ROWS_NARROW * _sm_count(device)
+
+
 # The LayerNorm epilogue needs a whole row in one tile, i.e. one CTA per 128 rows: below this many
 # rows per SM the separate kernels (narrower tiles, more CTAs) are faster.
 LN_FUSION_MIN_ROWS_PER_SM = 64

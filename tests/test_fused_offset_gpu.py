@@ -93,13 +93,19 @@ def test_module_with_fused_offsets_matches_module_without(dtype):
     m = m.to(dtype).eval()
     x = torch.randn(3, 14 * 14, 128, device=DEV).to(dtype)
     saved = ops.FUSED_OFFSET_MASK
+    calls = []
+    fused_op = ops.dcnv4_fused_offset_forward
     try:
+        ops.dcnv4_fused_offset_forward = lambda *a, **k: (calls.append(1), fused_op(*a, **k))[1]
         with torch.no_grad():
             ops.FUSED_OFFSET_MASK = True
             y_fused = m(x)
+            assert calls, "a 128-channel layer at inference takes the fused kernel"
             ops.FUSED_OFFSET_MASK = False
             y_plain = m(x)
+            assert len(calls) == 1
     finally:
         ops.FUSED_OFFSET_MASK = saved
+        ops.dcnv4_fused_offset_forward = fused_op
     close(y_fused, y_plain, FWD_TOL[dtype], "module, fused offsets vs separate Linear")
     assert ops.device_status() == 0
