@@ -454,6 +454,59 @@ def time_config0(torch, lib, dev, reps=200):
             "fwd_bwd_ms": fb_ms, "fwd_bwd_gbs": (fb + bb) / fb_ms / 1e6, "launches_back_to_back": reps}
 
 
+def time_fused_offset(torch, dev, batch=256, reps=20):
+    """The DCNv4 module's inference path around the operator at the four FlashInternImage-T stage shapes,
+    fp16: value projection + forward that computes its offset/mask rows itself, against both projections
+    as one product + stand-alone forward.  Each two-kernel sequence is captured in a CUDA graph (as the
+    model's forward is) and replayed `reps` times between two events; at batch 256 the tensors of one
+    replay exceed L2 at the first two stages."""
+    from dcnv4_b200 import ops
+    rows = []
+    for side, C, G in STAGES:
+        P, h = (27 * G + 7) // 8 * 8, torch.float16
+        gen = torch.Generator(device=dev).manual_seed(side)
+        x = torch.randn(batch, side * side, C, device=dev, generator=gen).to(h)
+        wv = (torch.randn(C, C, device=dev, generator=gen) / C ** 0.5).to(h)
+        wo = (torch.randn(P, C, device=dev, generator=gen) / C ** 0.5).to(h)
+        bv, bo = torch.zeros(C, device=dev, dtype=h), torch.randn(P, device=dev, generator=gen).to(h)
+        wcat, bcat = torch.cat([wv, wo]).contiguous(), torch.cat([bv, bo]).contiguous()
+
+        def two_step():
+            v, om = ops.linear_pair_forward(x, wcat, bcat, C)
+            return ops.dcnv4_forward(v.view(batch, side, side, C), om.view(batch, side, side, P), 3, 3, 1, 1, 1, 1,
+                                     1, 1, G, D, 1.0, 256, 0)
+
+        def fused():
+            v = ops.linear_forward(x, wv, bv)
+            return ops.dcnv4_fused_offset_forward(v.view(batch, side, side, C), x, wo, bo, G, D, 1.0)
+
+        def timed(fn):
+            side_stream = torch.cuda.Stream(device=dev)
+            side_stream.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side_stream):
+                for _ in range(3):
+                    fn()
+            torch.cuda.current_stream(dev).wait_stream(side_stream)
+            torch.cuda.synchronize(dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn()
+            for _ in range(3):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            return e0.elapsed_time(e1) / reps
+
+        same = bool(torch.equal(two_step(), fused()))
+        rows.append({"shape": f"{batch}x{side}x{side}x{C}, G={G}", "two_step_ms": timed(two_step),
+                     "fused_ms": timed(fused), "bit_identical": same})
+    return rows
+
+
 def _note(msg):
     """Progress note on stderr (stdout carries only the JSON line)."""
     if os.environ.get("RANK", "0") == "0":
@@ -676,6 +729,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.case and not args.no_fda:
         fda_ops = time_flash_deform_attn(torch, lib, dev, with_reference=not args.no_ref_cuda)
     config0 = time_config0(torch, lib, dev) if rank == 0 and not args.case else None
+    fused_rows = time_fused_offset(torch, dev) if rank == 0 and world == 1 and not args.case and not args.no_model else None
     if rank == 0:
         sampler.stop()
 
@@ -726,6 +780,7 @@ def run_ours(args):
             "config0_gpu": config0,
             "reference_cuda": ref_cuda_ops,
             "flash_deform_attn": fda_ops,
+            "fused_offset_forward": fused_rows,
             "flash_intern_image_t": None if model_ms != model_ms else {
                 "img_per_s": model_batch * world / model_ms * 1e3, "ms_per_batch": model_ms,
                 "batch_per_gpu": model_batch, "global_batch": model_batch * world, "dtype": "fp16",

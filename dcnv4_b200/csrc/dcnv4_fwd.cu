@@ -188,6 +188,8 @@ static cudaError_t launch_v(const T* value, const T* om, T* out, const DcnParams
   const long long n_tiles = (long long)p.N * p.tiles_x * p.tiles_y;
   const long long want = (long long)p.sm_count * per_sm;
   const int grid = (int)(n_tiles < want ? n_tiles : want);
+  if (plain) prefer_carveout<dcnv4_fwd_kernel<T, V, true>>((size_t)per_sm * (smem + 1024));
+  else prefer_carveout<dcnv4_fwd_kernel<T, V, false>>((size_t)per_sm * (smem + 1024));
   return launch_overlapped(kern, dim3((unsigned)grid), dim3(kThreads), smem, s, value, om, out, p, status);
 }
 

@@ -10,7 +10,8 @@
 // kernel reads.  Here the rows of 128 consecutive queries are computed on the tensor cores inside the
 // CTA that samples for them and never leave the SM.
 //
-// A task is 128 consecutive queries x 4 groups.  The 27 columns of a group (nine
+// A task is 128 consecutive queries x 4 groups (the last task of a query tile has fewer when the group
+// count is not a multiple of 4).  The 27 columns of a group (nine
 // (dx, dy) pairs, then nine masks) occupy a slot of 32 accumulator columns: the rows of W that belong
 // to a group are loaded as a 32-row box of their own, so a task's product is 128 x 128 and
 // every group starts on a 32-column boundary of tensor memory.  One persistent CTA per SM, eighteen
@@ -198,7 +199,7 @@ dcnv4_fwd_fused_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       const T* bias = static_cast<const T*>(p.bias);
       for (int i = wtid; i < p.bias_floats; i += kWorkThreads) {
         const int g = i / 28, c = i - g * 28;
-        s_bias[i] = (bias != nullptr && c < kPts) ? to_f32(bias[g * kPts + c]) : 0.f;
+        s_bias[i] = (bias != nullptr && c < kPts && g < p.G) ? to_f32(bias[g * kPts + c]) : 0.f;
       }
     }
     work_barrier();
@@ -248,7 +249,7 @@ dcnv4_fwd_fused_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       for (int item = tl; item < 32 * GC; item += 128) {
         const int ql = item / GC, gl = item % GC;
         const int q = mt * kQ + quad * 32 + ql;  // M < 2^31 - 128 (checked by the caller)
-        if (q >= (int)p.M) continue;
+        if (q >= (int)p.M || ch * GC + gl >= p.G) continue;
         int b = HW == 1 ? q : (int)__umulhi((uint32_t)q, mul_hw);
         int r = q - b * HW;
         if (r < 0) { --b; r += HW; }
@@ -302,8 +303,8 @@ dcnv4_fwd_fused_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 template <typename T, int GC>
 cudaError_t launch_gc(int dtype, const void* value, const void* x, const void* w, void* out, FusedParams p, int w_rows,
                       int K, int sms, cudaStream_t stream) {
-  p.chunks = p.G / GC;
-  p.bias_floats = 28 * p.G;
+  p.chunks = (p.G + GC - 1) / GC;  // a ragged last task computes columns of groups that do not exist
+  p.bias_floats = 28 * GC * p.chunks;
   p.stages = ring_stages(p.k_blocks);
   const size_t smem = fused_smem<GC>(p.bias_floats, p.stages);
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
@@ -322,6 +323,7 @@ cudaError_t launch_gc(int dtype, const void* value, const void* x, const void* w
     return cudaErrorNotSupported;
   const long long tasks = (long long)p.m_tiles * p.chunks;
   const int grid = (int)(tasks < sms ? tasks : sms);
+  prefer_carveout<dcnv4_fwd_fused_kernel<T, GC>>(smem + 1024);
   return launch_overlapped(dcnv4_fwd_fused_kernel<T, GC>, dim3((unsigned)grid), dim3(kFusedThreads), smem, stream, mx,
                            mw, static_cast<const T*>(value), static_cast<T*>(out), p);
 }
@@ -329,7 +331,7 @@ cudaError_t launch_gc(int dtype, const void* value, const void* x, const void* w
 }  // namespace
 
 bool dcnv4_fwd_fused_applies(int dtype, int G, int D, int K, int w_rows) {
-  return (dtype == 1 || dtype == 2) && D == 16 && G > 0 && G % 4 == 0 && K > 0 && K % 8 == 0 &&
+  return (dtype == 1 || dtype == 2) && D == 16 && G > 0 && K > 0 && K % 8 == 0 &&
          w_rows >= kPts * G && G <= 128;
 }
 

@@ -98,13 +98,14 @@ class DCNv4(nn.Module):
                 and ops.center_scale_blend_supported(x, w, self.group_channels))
 
     def _offsets_fusable(self, input) -> bool:
-        needs_grad = torch.is_grad_enabled() and (input.requires_grad or self.offset_mask.weight.requires_grad
-                                                  or self.value_proj.weight.requires_grad)
+        """Inference on 16-bit CUDA tensors in the configuration the fused kernel is written for (3x3,
+        stride 1, pad 1, dilation 1, all nine points, 16 channels per group), at a size where it pays."""
+        params = [self.offset_mask.weight] + ([] if self.without_pointwise else [self.value_proj.weight])
+        needs_grad = torch.is_grad_enabled() and (input.requires_grad or any(p.requires_grad for p in params))
         return (ops.fused_offset_pays(input.numel() // input.shape[-1], self.channels, input.device)
                 and not needs_grad and not torch.is_autocast_enabled()
-                and not self.without_pointwise and self.dw_kernel_size is None and not self.center_feature_scale
                 and not self.remove_center and self.kernel_size == 3 and self.stride == 1 and self.pad == 1
-                and self.dilation == 1 and self.group_channels == 16 and self.group % 4 == 0
+                and self.dilation == 1 and self.group_channels == 16
                 and input.is_cuda and input.is_contiguous()
                 and input.dtype in (torch.float16, torch.bfloat16) and self.offset_mask.weight.dtype == input.dtype)
 
@@ -120,23 +121,16 @@ class DCNv4(nn.Module):
         else:
             H, W = int(L ** 0.5), int(L ** 0.5)
 
-        if self._offsets_fusable(input):
-            # inference: the offset/mask rows are produced by the sampling kernel itself
-            x = ops.linear_module_forward(input, self.value_proj).reshape(N, H, W, -1)
-            if ops.fused_offset_supported(x, input, self.offset_mask.weight, self.offset_mask.bias, self.group,
-                                          self.group_channels):
-                x = ops.dcnv4_fused_offset_forward(x, input, self.offset_mask.weight, self.offset_mask.bias,
-                                                   self.group, self.group_channels, self.offset_scale)
-                return ops.linear_module_forward(x.view(N, L, -1), self.output_proj, residual, "none", norm)
-
+        fuse = self._offsets_fusable(input)
         paired = None
-        if not self.without_pointwise and self.dw_kernel_size is None:
+        if not fuse and not self.without_pointwise and self.dw_kernel_size is None:
             # both projections read the layer input: at inference they are one tensor-core product
             paired = self.__dict__.get("_paired_proj")
             if paired is None or paired.first is not self.value_proj or paired.second is not self.offset_mask:
                 paired = self.__dict__["_paired_proj"] = ops.PairedLinear(self.value_proj, self.offset_mask)
             if not (input.is_contiguous() and paired.usable(input)):
                 paired = None
+        offset_mask = offset_mask_input = None
         if paired is not None:
             x, offset_mask = paired(input)
             x = x.reshape(N, H, W, -1)
@@ -144,20 +138,30 @@ class DCNv4(nn.Module):
         else:
             x = input
             if not self.without_pointwise:
-                x = self.value_proj(x)
+                x = ops.linear_module_forward(x, self.value_proj) if fuse else self.value_proj(x)
             x = x.reshape(N, H, W, -1)
             if self.dw_kernel_size is not None:
                 offset_mask_input = self.offset_mask_dw(input.view(N, H, W, C).permute(0, 3, 1, 2))
-                offset_mask_input = offset_mask_input.permute(0, 2, 3, 1).view(N, L, C)
+                offset_mask_input = offset_mask_input.permute(0, 2, 3, 1).reshape(N, L, C)
             else:
                 offset_mask_input = input
-            offset_mask = self.offset_mask(offset_mask_input).reshape(N, H, W, -1)
+            # inference: the sampling kernel computes the offset/mask rows itself from the Linear's input
+            if fuse and not offset_mask_input.is_contiguous():
+                offset_mask_input = offset_mask_input.contiguous()
+            fuse = fuse and ops.fused_offset_supported(x, offset_mask_input, self.offset_mask.weight,
+                                                       self.offset_mask.bias, self.group, self.group_channels)
+            if not fuse:
+                offset_mask = self.offset_mask(offset_mask_input).reshape(N, H, W, -1)
 
         x_proj = x
-        x = DCNv4Function.apply(
-            x, offset_mask, self.kernel_size, self.kernel_size, self.stride, self.stride,
-            self.pad, self.pad, self.dilation, self.dilation, self.group, self.group_channels,
-            self.offset_scale, 256, self.remove_center)
+        if offset_mask is None:
+            x = ops.dcnv4_fused_offset_forward(x, offset_mask_input, self.offset_mask.weight, self.offset_mask.bias,
+                                               self.group, self.group_channels, self.offset_scale)
+        else:
+            x = DCNv4Function.apply(
+                x, offset_mask, self.kernel_size, self.kernel_size, self.stride, self.stride,
+                self.pad, self.pad, self.dilation, self.dilation, self.group, self.group_channels,
+                self.offset_scale, 256, self.remove_center)
 
         if self.center_feature_scale and self._blend_fusable(x, x_proj):
             # inference: Linear + sigmoid + repeat + blend in one pass over x and x_proj

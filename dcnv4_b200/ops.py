@@ -344,7 +344,7 @@ def fused_offset_supported(value: torch.Tensor, x: torch.Tensor, weight: torch.T
         return False
     N, H, W, C = value.shape
     rows, K = weight.shape
-    return (group_channels == 16 and C == 16 * group and group % 4 == 0 and group <= 128
+    return (group_channels == 16 and C == 16 * group and 0 < group <= 128
             and K % 8 == 0 and x.shape[-1] == K and x.numel() == N * H * W * K and rows >= 27 * group
             and value.numel() < 2 ** 31)
 

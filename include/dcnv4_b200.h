@@ -242,7 +242,7 @@ int dcnv4b200_linear_pair_fwd(const void* x, const void* weight, const void* bia
  * (DCNv4_op/DCNv4/modules/dcnv4.py:121-140) with the (N, H, W, padded 27 G) tensor between them.
  *   value, out (N, H, W, G*D), 32-byte aligned; x (N*H*W, K) and weight (weight_rows, K) row-major,
  *   16-byte aligned; bias (weight_rows) or NULL; all fp16 or all bf16.
- *   D must be 16 and G a multiple of 4 up to 128 (DCNV4B200_ERR_UNSUPPORTED otherwise: the caller
+ *   D must be 16 and G at most 128 (DCNV4B200_ERR_UNSUPPORTED otherwise: the caller
  *   then runs the two steps separately); K a multiple of 8; weight_rows >= 27 G
  *   (_ERR_PADDED_DIM), rows beyond 27 G -- the Linear's padding -- are ignored.
  */
