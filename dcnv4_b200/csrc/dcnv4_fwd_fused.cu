@@ -11,11 +11,10 @@
 // CTA that samples for them and never leave the SM.
 //
 // A task is 128 consecutive queries x 4 groups (the last task of a query tile has fewer when the group
-// count is not a multiple of 4).  The 27 columns of a group (nine
-// (dx, dy) pairs, then nine masks) occupy a slot of 32 accumulator columns: the rows of W that belong
-// to a group are loaded as a 32-row box of their own, so a task's product is 128 x 128 and
-// every group starts on a 32-column boundary of tensor memory.  One persistent CTA per SM, eighteen
-// warps:
+// count is not a multiple of 4).  The 27 columns of a group (nine (dx, dy) pairs, then nine masks)
+// occupy a slot of 32 accumulator columns: the rows of W that belong to a group are loaded as a 32-row
+// box of their own, so a task's product is 128 x 128 and every group starts on a 32-column boundary of
+// tensor memory.  One persistent CTA per SM, eighteen warps:
 //   warp 0     producer : TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle, this GPU's memory, no
 //                         multicast) of the x tile (128 x 64) and of four boxes of W (32 x 64 each) into
 //                         a shared-memory ring, one slot per 64 input features;
@@ -35,9 +34,10 @@
 //                         one 32-byte load per bilinear corner, fp32 arithmetic, one 32-byte store of
 //                         the 16 output channels.  The offset/mask rows never reach global memory.
 // Every mbarrier wait is bounded.  A worker warp whose wait runs out records kStatusStageTimeout and
-// raises a flag that its team reads after the next barrier (the flag is only written between the two
-// barriers of a task), so the team leaves the loop together and no warp is left waiting at a barrier; the producer and the MMA lane stop on their own
-// bounded waits, and the CTA frees its tensor memory.
+// raises its team's flag; the flag is only ever written before the first of a task's two team barriers
+// and read right after it, so the team leaves the loop together and no warp is left waiting at a
+// barrier.  The producer and the MMA lane stop on their own bounded waits, and the CTA frees its tensor
+// memory.
 #include <mutex>
 
 #include "gelu_table.cuh"
