@@ -140,14 +140,20 @@ dcnv4_fwd_fused_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   pdl_trigger();
   pdl_wait();  // x and value are earlier kernels' outputs; out may still be read by one
 
+  // Each CTA takes a contiguous share of the tasks (shares differ by at most one): consecutive tasks are
+  // the next groups of the same queries and then the next 128 queries, about two image rows further down,
+  // whose samples fall on rows this SM's L1 still holds.
   const long long n_tasks = (long long)p.m_tiles * p.chunks;
+  const long long share = n_tasks / gridDim.x, extra = n_tasks % gridDim.x;
+  const long long t_begin = blockIdx.x * share + (blockIdx.x < extra ? blockIdx.x : extra);
+  const long long t_end = t_begin + share + (blockIdx.x < extra ? 1 : 0);
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (long long t = blockIdx.x; t < n_tasks && !*abort_flag; t += gridDim.x) {
+      for (long long t = t_begin; t < t_end && !*abort_flag; ++t) {
         const int mt = (int)(t / p.chunks), ch = (int)(t - (long long)mt * p.chunks);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_bounded(&empty[stage], phase ^ 1)) { atomicExch(p.status, kStatusStageTimeout); *abort_flag = 1; break; }
@@ -168,7 +174,7 @@ dcnv4_fwd_fused_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       constexpr uint32_t idesc = instr_desc<T>(BN, kQ);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
-      for (long long t = blockIdx.x; t < n_tasks && !*abort_flag; t += gridDim.x) {
+      for (long long t = t_begin; t < t_end && !*abort_flag; ++t) {
         if (!mbar_wait_bounded(&acc_empty[acc], acc_phase ^ 1)) { atomicExch(p.status, kStatusStageTimeout); *abort_flag = 1; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -211,7 +217,7 @@ dcnv4_fwd_fused_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     const uint32_t mul_hw = (uint32_t)(0x100000000ull / (uint32_t)HW) + 1u;
     const uint32_t mul_w = (uint32_t)(0x100000000ull / (uint32_t)p.W) + 1u;
     uint32_t it = 0;
-    for (long long t = blockIdx.x; t < n_tasks; t += gridDim.x, ++it) {
+    for (long long t = t_begin; t < t_end; ++t, ++it) {
       const int acc = (int)(it & 1);
       const uint32_t acc_phase = (it >> 1) & 1;
       const int mt = (int)(t / p.chunks), ch = (int)(t - (long long)mt * p.chunks);
