@@ -102,12 +102,12 @@ class DCNv4(nn.Module):
         stride 1, pad 1, dilation 1, all nine points, 16 channels per group), at a size where it pays."""
         params = [self.offset_mask.weight] + ([] if self.without_pointwise else [self.value_proj.weight])
         needs_grad = torch.is_grad_enabled() and (input.requires_grad or any(p.requires_grad for p in params))
-        return (ops.fused_offset_pays(input.numel() // input.shape[-1], self.channels, input.device)
+        return (input.is_cuda and input.is_contiguous() and input.numel() > 0
+                and input.dtype in (torch.float16, torch.bfloat16) and self.offset_mask.weight.dtype == input.dtype
                 and not needs_grad and not torch.is_autocast_enabled()
                 and not self.remove_center and self.kernel_size == 3 and self.stride == 1 and self.pad == 1
                 and self.dilation == 1 and self.group_channels == 16
-                and input.is_cuda and input.is_contiguous()
-                and input.dtype in (torch.float16, torch.bfloat16) and self.offset_mask.weight.dtype == input.dtype)
+                and ops.fused_offset_pays(input.numel() // input.shape[-1], self.channels, input.device))
 
     def forward(self, input, shape=None, residual=None, norm=None):
         """input (N, L, C) with L = H*W; `shape` = (H, W) when the map is not square.

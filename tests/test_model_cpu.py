@@ -133,3 +133,27 @@ def test_fused_projection_cache_is_dropped_when_parameters_may_have_changed_unse
         paired._weight = torch.zeros(1)
         action()
         assert paired._key is None and paired._weight is None
+
+
+def test_fused_offset_policy_thresholds(monkeypatch):
+    """The module fuses the offset/mask Linear into the sampling kernel from 128 channels up at any batch
+    and for narrower layers only when there are many rows per SM; the switch turns it off."""
+    from dcnv4_b200 import ops
+    monkeypatch.setattr(ops, "_sm_count", lambda device: 148)
+    monkeypatch.setattr(ops, "_FUSED_OFFSET_ENV", "")
+    monkeypatch.setattr(ops, "FUSED_OFFSET_MASK", True)
+    assert ops.fused_offset_pays(100, 128, "cuda:0")
+    assert ops.fused_offset_pays(256 * 56 * 56, 64, "cuda:0")
+    assert not ops.fused_offset_pays(64 * 56 * 56, 64, "cuda:0")
+    monkeypatch.setattr(ops, "_FUSED_OFFSET_ENV", "1")
+    assert ops.fused_offset_pays(1, 64, "cuda:0")
+    monkeypatch.setattr(ops, "FUSED_OFFSET_MASK", False)
+    assert not ops.fused_offset_pays(10 ** 9, 512, "cuda:0")
+
+
+def test_cpu_input_is_refused_by_the_operator_not_by_the_fusion_policy():
+    """No CPU fallback: a CPU tensor reaches the operator's own check (RuntimeError naming CUDA)."""
+    from dcnv4_b200.modules import DCNv4
+    m = DCNv4(channels=64, group=4).eval()
+    with torch.no_grad(), pytest.raises(RuntimeError, match="CUDA"):
+        m(torch.randn(1, 16, 64))
